@@ -267,11 +267,13 @@ def _parse_random(path: str):
         raw = preset(name)
     except KeyError as e:
         raise ErrUnknownFormat(f"gophonic_b200: {e.args[0]}") from None
-    if args["layers"] < 0 or args["layers"] > raw["num_hidden_layers"]:
-        raise ValueError(f"gophonic_b200: layers={args['layers']} of a configuration with {raw['num_hidden_layers']}")
+    config = registry.config_class(registry.architecture_of(raw)).from_dict(raw)
+    total = config.num_layers if hasattr(config, "num_layers") else config.num_hidden_layers
+    if args["layers"] < 0 or args["layers"] > total:
+        raise ValueError(f"gophonic_b200: layers={args['layers']} of a configuration with {total}")
     if args["layers"]:
-        raw = dict(raw, num_hidden_layers=args["layers"])
-    return registry.config_class(registry.architecture_of(raw)).from_dict(raw), args["seed"]
+        config = config.with_layers(args["layers"])
+    return config, args["seed"]
 
 
 def _open_random(path: str, opts: Options) -> OpenedModel:

@@ -7,8 +7,8 @@ Within a page the layout is [kv_head][64][head_dim], so one head's 64 keys are o
 block.  A block table [slot][logical page] -> physical page, mirrored on the device, is shared
 by every group: page p of a sequence is physical page table[slot][p] in every plane.
 
-Groups.  Runs of layers are grouped by what they need: (kv_heads, head_dim, window) for
-key/value planes, (shape, dtype) for fixed-size state.  Each group has storage of its own; a run
+Groups.  Runs of layers are grouped by what they need: (kv_heads, head_dim, window, value_dim) for
+key/value planes (a value head may have another size than a key head), (shape, dtype) for fixed-size state.  Each group has storage of its own; a run
 is given the plane with its ordinal inside its group (the reference indexes KV planes the same
 way, by a layer's place among layers of its kind: internal/qwen3lm/gpu_darwin.go:51-55, 270-277,
 831, and keeps per-sequence state beside K/V: gpu_darwin.go:800-808).  A run that reads another
@@ -147,7 +147,7 @@ class Cache:
         self.block_table[self.spare_slot, 0] = self.spare_page
 
         # groups
-        self._kv_groups: Dict[Tuple[int, int, int], List[int]] = {}
+        self._kv_groups: Dict[Tuple[int, ...], List[int]] = {}
         self._state_groups: Dict[Tuple[Tuple[int, ...], torch.dtype], List[int]] = {}
         self._plane: Dict[int, Tuple[str, object, int]] = {}
         self._cache_of: Dict[int, Optional[int]] = {}
@@ -156,7 +156,7 @@ class Cache:
             if cache_of is not None or req is None:
                 continue
             if isinstance(req, KVRequest):
-                key = (req.kv_heads, req.head_dim, req.window)
+                key = (req.kv_heads, req.head_dim, req.window, req.value_dim or req.head_dim)
                 planes = self._kv_groups.setdefault(key, [])
                 self._plane[pos] = ("kv", key, len(planes))
                 planes.append(pos)
@@ -170,13 +170,12 @@ class Cache:
         for pos, cache_of in self._cache_of.items():
             if cache_of is not None and cache_of not in self._plane:
                 raise CacheError(f"schedule position {pos} reads the cache of position {cache_of}, which has none")
-        self._k: Dict[Tuple[int, int, int], torch.Tensor] = {}
-        self._v: Dict[Tuple[int, int, int], torch.Tensor] = {}
+        self._k: Dict[Tuple[int, ...], torch.Tensor] = {}
+        self._v: Dict[Tuple[int, ...], torch.Tensor] = {}
         for key, planes in self._kv_groups.items():
-            kvh, d, _w = key
-            shape = (len(planes), self.n_pages + 1, kvh, PAGE, d)
-            self._k[key] = torch.zeros(shape, dtype=dtype, device=self.device)
-            self._v[key] = torch.zeros(shape, dtype=dtype, device=self.device)
+            kvh, d, _w, dv = key
+            self._k[key] = torch.zeros((len(planes), self.n_pages + 1, kvh, PAGE, d), dtype=dtype, device=self.device)
+            self._v[key] = torch.zeros((len(planes), self.n_pages + 1, kvh, PAGE, dv), dtype=dtype, device=self.device)
         self._state: Dict[Tuple[Tuple[int, ...], torch.dtype], torch.Tensor] = {}
         for key, planes in self._state_groups.items():
             shape, sdtype = key
@@ -192,9 +191,9 @@ class Cache:
     # ---- description -------------------------------------------------------------------
     def groups(self) -> List[dict]:
         out = []
-        for (kvh, d, w), planes in self._kv_groups.items():
-            out.append({"kind": "kv", "kv_heads": kvh, "head_dim": d, "window": w, "planes": list(planes),
-                        "bytes_per_token": 2 * len(planes) * kvh * d * torch.empty((), dtype=self.dtype).element_size()})
+        for (kvh, d, w, dv), planes in self._kv_groups.items():
+            out.append({"kind": "kv", "kv_heads": kvh, "head_dim": d, "value_dim": dv, "window": w, "planes": list(planes),
+                        "bytes_per_token": len(planes) * kvh * (d + dv) * torch.empty((), dtype=self.dtype).element_size()})
         for (shape, sdtype), planes in self._state_groups.items():
             out.append({"kind": "state", "shape": shape, "dtype": str(sdtype), "planes": list(planes)})
         return out
@@ -317,6 +316,17 @@ class Cache:
         while len(self._pages_of[slot]) > keep:
             self.pages.give(self._pages_of[slot].pop())
         self._length[slot] = n
+
+    def has_state(self) -> bool:
+        return bool(self._state)
+
+    def copy_state(self, slot: int) -> Dict[object, torch.Tensor]:
+        """A copy of the fixed-size state of ``slot`` (which may be the spare slot), for ``put_state``."""
+        return {key: t[:, slot].clone() for key, t in self._state.items()}
+
+    def put_state(self, slot: int, saved: Dict[object, torch.Tensor]) -> None:
+        for key, t in saved.items():
+            self._state[key][:, slot].copy_(t)
 
     def snapshot(self, slot: int) -> "CacheMark":
         """A mark of the sequence as it is: its length and a copy of its fixed-size state.  Keys and

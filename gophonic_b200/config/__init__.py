@@ -1,7 +1,9 @@
-from .spec import (AttentionSpec, EmbeddingSpec, HeadSpec, LayerSpec, ModelSpec, NoPositionSpec,
-                   RMSNormSpec, RotarySpec, ScheduleEntry, SwiGLUSpec, default_schedule)
+from .spec import (AttentionSpec, DecayStateSpec, EmbeddingSpec, GatedAttentionSpec, HeadSpec, LayerSpec,
+                   MatrixMemorySpec, ModelSpec, NoPositionSpec, PairRotarySpec, RMSNormSpec, RotarySpec,
+                   ScheduleEntry, SwiGLUSpec, default_schedule)
 from .qwen3 import ConfigError, Qwen3Config
+from .pugalix import PugalixConfig
 
-__all__ = ["AttentionSpec", "EmbeddingSpec", "HeadSpec", "LayerSpec", "ModelSpec", "NoPositionSpec",
-           "RMSNormSpec", "RotarySpec", "ScheduleEntry", "SwiGLUSpec", "default_schedule",
-           "ConfigError", "Qwen3Config"]
+__all__ = ["AttentionSpec", "DecayStateSpec", "EmbeddingSpec", "GatedAttentionSpec", "HeadSpec", "LayerSpec",
+           "MatrixMemorySpec", "ModelSpec", "NoPositionSpec", "PairRotarySpec", "RMSNormSpec", "RotarySpec",
+           "ScheduleEntry", "SwiGLUSpec", "default_schedule", "ConfigError", "Qwen3Config", "PugalixConfig"]

@@ -147,6 +147,11 @@ class Qwen3Config:
             "torch_dtype": self.torch_dtype,
         }
 
+    def with_layers(self, n: int) -> "Qwen3Config":
+        """The same configuration with ``n`` layers (every layer keeps its size)."""
+        from dataclasses import replace
+        return replace(self, num_hidden_layers=n)
+
     # ---- derived -------------------------------------------------------------------------
     @property
     def q_dim(self) -> int:

@@ -19,10 +19,12 @@ from typing import Optional, Sequence, Tuple
 
 @dataclass(frozen=True)
 class RMSNormSpec:
-    """y = x * rsqrt(mean(x^2) + eps) * weight  (internal/qwen3lm/ops.go:251-254)."""
+    """y = x * rsqrt(mean(x^2) + eps) * weight  (internal/qwen3lm/ops.go:251-254).  The weight is
+    the tensor ``prefix + tensor``."""
     size: int
     eps: float
     kind: str = "rmsnorm"
+    tensor: str = "weight"
 
 
 @dataclass(frozen=True)
@@ -36,6 +38,17 @@ class RotarySpec:
     rotary_dim: int
     theta: float
     kind: str = "rope"
+
+
+@dataclass(frozen=True)
+class PairRotarySpec:
+    """Rotary embedding in which neighbouring channels turn together: channels 2i and 2i + 1 of a
+    head, i < rotary_dim / 2, by the angle pos * theta^(-2i/rotary_dim); the channels from
+    ``rotary_dim`` on pass unchanged."""
+    head_dim: int
+    rotary_dim: int
+    theta: float
+    kind: str = "rope_pairs"
 
 
 @dataclass(frozen=True)
@@ -64,11 +77,80 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class GatedAttentionSpec:
+    """Grouped-query attention with the options of the Pugalix design, each of which can be left off:
+
+    * ``bias``: q, k and v projections carry a bias;
+    * ``value_dim``: a value head may have another size than a query/key head;
+    * ``window`` > 0 with ``keep_first``: position i sees j <= i if i - j < window or j < keep_first;
+    * ``sink``: the softmax denominator carries one more unit, p_j = exp(s_j) / (1 + sum exp(s));
+    * ``gate``: the concatenated heads are multiplied by sigmoid of a further projection of the
+      mixer's input before the output projection;
+    * ``own_kv`` False: the layer has no key/value projections and reads the cache plane of an
+      earlier run (``ScheduleEntry.cache_of``), with queries, mask and the rest of its own.
+
+    ``names`` maps q, k, v, g, o to tensor-name suffixes under the mixer's prefix; a bias is the
+    projection's name plus ``bias_suffix``."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    position: object
+    window: int = 0
+    keep_first: int = 0
+    sink: bool = False
+    bias: bool = False
+    gate: bool = False
+    own_kv: bool = True
+    names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("k", "k"), ("v", "v"), ("g", "g"), ("o", "o"))
+    bias_suffix: str = ".b"
+    kind: str = "gated_attention"
+
+
+@dataclass(frozen=True)
+class DecayStateSpec:
+    """Gated linear attention: per head a matrix state S (key_dim x value_dim, float32) with a decay
+    per key channel, S <- diag(a) S + k v^T, o = S^T q, q scaled by key_dim^(-1/2).  The decay is
+    a = sigmoid(W2 (W1 x) + b)^(1 / tau) with W1 of ``rank`` rows.  Each head's o is RMS-normed with
+    one weight of ``value_dim`` shared by the heads, multiplied by silu of a gate projection, and
+    projected back."""
+    hidden: int
+    heads: int
+    key_dim: int
+    value_dim: int
+    rank: int
+    tau: float
+    eps: float
+    kind: str = "gla"
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec:
+    """The matrix memory of an mLSTM: per head S (key_dim x value_dim), a normaliser n (key_dim) and a
+    running maximum m, all float32 and zero at the start.  With log gates i = cap tanh(x_i / cap) and
+    f = logsigmoid(cap tanh(x_f / cap)): m' = max(f + m, i), S <- exp(f + m - m') S + exp(i - m') k v^T,
+    n likewise with k alone, o = S^T q / (max(|n . q|, exp(-m')) + 1e-6), q scaled by key_dim^(-1/2).
+    Each head's o is divided by its root mean square; the heads together are multiplied by a weight
+    and by sigmoid of a gate projection, and projected back."""
+    hidden: int
+    heads: int
+    key_dim: int
+    value_dim: int
+    gate_cap: float
+    eps: float
+    kind: str = "mlstm"
+
+
+@dataclass(frozen=True)
 class SwiGLUSpec:
-    """down(silu(gate(x)) * up(x))  (internal/qwen3lm/ops.go:442-461)."""
+    """down(silu(gate(x)) * up(x))  (internal/qwen3lm/ops.go:442-461).  ``names``: the tensors of the
+    gate, up and down projections under the part's prefix."""
     hidden: int
     intermediate: int
     kind: str = "swiglu"
+    names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
 
 
 @dataclass(frozen=True)
@@ -82,7 +164,8 @@ class LayerSpec:
     ``prefix``; everything else is between the spec and the block class registered under that
     kind (``declare``, ``cache_request``, ``mixers``, ``prepare``, ``weight_bytes``, ``forward``).
     A block with another arrangement (one shared norm, norms after the parts, two mixers) brings a
-    spec class of its own with those two fields.
+    spec class of its own with those two fields.  ``feed_forward`` and ``feed_forward_norm`` None:
+    the layer is its mixer sublayer alone.
     """
     prefix: str
     mixer: object
@@ -111,9 +194,11 @@ class ScheduleEntry:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
+    """``scale`` multiplies every embedding row as it enters the float32 residual."""
     name: str
     vocab: int
     hidden: int
+    scale: float = 1.0
 
 
 @dataclass(frozen=True)

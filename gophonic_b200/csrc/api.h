@@ -34,6 +34,9 @@ struct AttnParams {
     float* scratch;  // [nseq][heads][num_splits][d + 2] when num_splits > 1
     int pages;       // pages of each cache plane, and slots (rows) of the block table: the bounds the
     int max_slots;   // checked build holds every page and slot index against
+    int dv;          // size of a value head; 0: the same as d.  Only the CUDA-core kernel takes another size.
+    int keep_first;  // with a window: keys at positions below this stay visible however far back they lie
+    int sink;        // 1: the softmax denominator carries one more unit (a key of score 0 without a value)
 };
 
 // Per-head q/k RMSNorm, rotary embedding and cache write on the rows of a fused q|k|v buffer.
@@ -58,6 +61,55 @@ struct QkRopeParams {
     int rows, heads, kv_heads, d;
     int pages;      // pages of each cache plane, and slots (rows) of the block table: the bounds the
     int max_slots;  // checked build holds every page and slot index against
+    // what only the general kernel takes (null / 0: absent)
+    const float* q_b;  // biases added to the heads before norm and rotation: [heads * d], [kv_heads * d], [kv_heads * dv]
+    const float* k_b;
+    const float* v_b;
+    int pairs;         // 1: channels 2j and 2j + 1 turn together by angle j; 0: channels j and j + rot / 2
+    int dv;            // size of a value head; 0: the same as d
+};
+
+// A matrix state per (sequence, head), updated token by token: S <- diag(a) S + b k v^T, o = S^T q.
+struct LinearStateParams {
+    const void* qkv;        // rows of the fused projection (activation dtype): q, k and v heads at the offsets below
+    int64_t row_stride;
+    int q_off, k_off, v_off;
+    float q_scale;          // q is multiplied by this as it is read
+    const float* decay;     // per key channel: [rows, decay_stride] holding heads x d factors (scalar_decay 0)
+    int64_t decay_stride;
+    const float* gates;     // scalar_decay 1: pre-activations of the input gates [heads] then the forget gates [heads] of every row
+    int64_t gates_stride;
+    const float* gate_bias; // [2 heads] or null
+    float gate_cap;         // gates are capped as cap * tanh(x / cap)
+    float* coef;            // scalar_decay 1: [rows, heads, 4] scratch (keep, take, running maximum, divisor)
+    float* state;           // [slots, ...]: per head d x dv of S, then (scalar_decay 1) d of the normaliser and the maximum
+    int64_t slot_stride, head_stride;
+    float* out;             // [rows, out_stride]: heads x dv sums S^T q (not yet divided)
+    int64_t out_stride;
+    const int* seq_slot;
+    const int* seq_q_start;
+    const int* seq_q_len;
+    int nseq, heads, d, dv;
+    int scalar_decay;
+    int max_slots;
+};
+
+// y = norm(x / divisor) * weight * gate(g) per (row, head); one warp a head.
+struct HeadGateParams {
+    const void* x;          // [rows, x_stride]: heads x size
+    int64_t x_stride;
+    const void* gate;       // [rows, gate_stride]: heads x size pre-activations of the gate (activation dtype)
+    int64_t gate_stride;
+    void* y;                // [rows, y_stride] (activation dtype)
+    int64_t y_stride;
+    const float* divisor;   // [rows, heads, divisor_stride] (its first element is used) or null
+    int divisor_stride;
+    const float* weight;    // [size] or [heads x size] or null
+    int weight_per_head;
+    int normed;             // 1: x over its root mean square (eps under the root) first
+    float eps;
+    int gate_kind;          // 0: sigmoid(g); 1: g * sigmoid(g)
+    int rows, heads, size;
 };
 
 GB_API const char* gb_last_error();
@@ -95,3 +147,8 @@ GB_API int gb_attention_prefill_mma(const AttnParams* p, cudaStream_t stream);
 GB_API int gb_attention_decode_rope_accepts(int dtype, int d, int rot, int max_q_len);
 GB_API int gb_attention_decode_mma_rope(const AttnParams* p, const QkRopeParams* r, cudaStream_t stream);
 GB_API int gb_attention_prefill_tc5(const AttnParams* p, int rows, int pages, cudaStream_t stream);
+
+// matrix-state mixers
+GB_API int gb_gla_decay(float* z, const float* bias, int rows, int width, float tau, cudaStream_t stream);
+GB_API int gb_state_scan(const LinearStateParams* p, int dtype, cudaStream_t stream);
+GB_API int gb_head_norm_gate(const HeadGateParams* p, int x_dtype, int dtype, cudaStream_t stream);

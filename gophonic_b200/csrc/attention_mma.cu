@@ -20,7 +20,7 @@
 
 
 int gb_attention_merge_launch(const float* scratch, void* out, int dtype, int64_t out_row_stride, const int* seq_q_start,
-                              int nseq, int heads, int d, int num_splits, cudaStream_t stream);
+                              int nseq, int heads, int d, int num_splits, int sink, cudaStream_t stream);
 
 namespace {
 
@@ -595,7 +595,7 @@ int launch_decode(const AttnParams& p, const RopeFuse& f, cudaStream_t stream) {
     GB_CHECK_LAUNCH("attention_decode_mma");
     if (p.num_splits > 1)
         return gb_attention_merge_launch(p.scratch, p.out, GB_BF16, p.out_row_stride, p.seq_q_start, p.nseq, p.heads, p.d,
-                                         p.num_splits, stream);
+                                         p.num_splits, 0, stream);
     return 0;
 }
 
@@ -604,6 +604,8 @@ int check(const AttnParams& p, const char* who) {
     if (p.d % 16 || p.d < 16 || (p.d > 128 && p.d != 256))
         GB_REFUSE("%s: head_dim %d is not one of 16, 32, ..., 128, 256 (other sizes up to 256 run on the CUDA-core kernel)", who, p.d);
     if (p.window < 0) GB_REFUSE("%s: window %d", who, p.window);
+    if ((p.dv && p.dv != p.d) || p.keep_first || p.sink)
+        GB_REFUSE("%s: values of another size than keys, kept first tokens and a sink run on the CUDA-core kernel", who);
     if (((uintptr_t)p.q & 15) || (p.q_row_stride & 7)) GB_REFUSE("%s: query rows must be 16-byte aligned", who);
     if ((p.out_row_stride & 1) || ((uintptr_t)p.out & 3)) GB_REFUSE("%s: output rows must be 4-byte aligned", who);
     return 0;
@@ -671,6 +673,7 @@ GB_API int gb_attention_decode_mma_rope(const AttnParams* pp, const QkRopeParams
     if (r.write_kv && (r.k_plane != p.k_plane || r.v_plane != p.v_plane)) GB_REFUSE("%s: keys would be written to another plane than is read", who);
     if (!gb_attention_decode_rope_accepts(GB_BF16, p.d, r.rot, p.max_q_len)) GB_REFUSE("%s: head_dim %d, rotary width %d", who, p.d, r.rot);
     if (r.rot > 0 && (!r.cos_t || !r.sin_t)) GB_REFUSE("%s: rotary width %d without an angle table", who, r.rot);
+    if (r.q_b || r.k_b || r.v_b || r.pairs || (r.dv && r.dv != r.d)) GB_REFUSE("%s: biases, rotation by pairs and values of another size are the row-wise kernel's", who);
     RopeFuse f = {};
     f.on = 1;
     f.q_w = r.q_w;

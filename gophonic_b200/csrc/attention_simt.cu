@@ -24,9 +24,10 @@ template <typename T, int NE>
 __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
     extern __shared__ float sm[];
     const int d = p.d, ks = d + 1;
+    const int dv = p.dv > 0 ? p.dv : p.d, vs = dv + 1;   // values may be narrower or wider than keys
     float* Qs = sm;                // [16][d], pre-scaled
     float* Ks = Qs + ROWS * d;     // [32][d + 1]
-    float* Vs = Ks + KT * ks;      // [32][d + 1]
+    float* Vs = Ks + KT * ks;      // [32][dv + 1]
 
     const int G = p.heads / p.kv_heads;
     const int GC = G < ROWS ? G : ROWS;
@@ -76,9 +77,15 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
         if (lo_pos < 0) lo_pos = 0;
     }
     const int t_lo = lo_pos / KT, t_hi = hi_pos / KT + 1;
-    const int per = (t_hi - t_lo + p.num_splits - 1) / p.num_splits;
-    const int my_lo = t_lo + split * per;
-    const int my_hi = my_lo + per < t_hi ? my_lo + per : t_hi;
+    // With kept first tokens the tiles visited are those of keys [0, keep_first) and then those of the
+    // window, each once and in order of position: tile index i < n_first is tile i, the others follow
+    // from t_lo.
+    int n_first = p.window > 0 && p.keep_first > 0 ? (p.keep_first + KT - 1) / KT : 0;
+    if (n_first > t_lo) n_first = t_lo;
+    const int n_tiles = n_first + (t_hi - t_lo);
+    const int per = (n_tiles + p.num_splits - 1) / p.num_splits;
+    const int my_lo = split * per;
+    const int my_hi = my_lo + per < n_tiles ? my_lo + per : n_tiles;
 
     float m[RW], l[RW], acc[RW][NE];
 #pragma unroll
@@ -89,7 +96,8 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
         for (int e = 0; e < NE; e++) acc[rr][e] = 0.f;
     }
 
-    for (int t = my_lo; t < my_hi; t++) {
+    for (int ti = my_lo; ti < my_hi; ti++) {
+        const int t = ti < n_first ? ti : t_lo + (ti - n_first);
         __syncthreads();
         // each warp stages 8 keys of the tile
         for (int jj = 0; jj < 8; jj++) {
@@ -97,18 +105,14 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
             int key = t * KT + j;
             if (key <= hi_pos) {
                 int64_t page = page_of(bt, key, p.bt_stride, p.pages);
-                int64_t off = ((page * p.kv_heads + kvh) * GB_PAGE + (key % GB_PAGE)) * (int64_t)d;
-                const T* kp = (const T*)p.k_plane + off;
-                const T* vp = (const T*)p.v_plane + off;
-                for (int c = lane; c < d; c += 32) {
-                    Ks[j * ks + c] = to_f32<T>(kp[c]);
-                    Vs[j * ks + c] = to_f32<T>(vp[c]);
-                }
+                int64_t at = (page * p.kv_heads + kvh) * GB_PAGE + (key % GB_PAGE);
+                const T* kp = (const T*)p.k_plane + at * (int64_t)d;
+                const T* vp = (const T*)p.v_plane + at * (int64_t)dv;
+                for (int c = lane; c < d; c += 32) Ks[j * ks + c] = to_f32<T>(kp[c]);
+                for (int c = lane; c < dv; c += 32) Vs[j * vs + c] = to_f32<T>(vp[c]);
             } else {
-                for (int c = lane; c < d; c += 32) {
-                    Ks[j * ks + c] = 0.f;
-                    Vs[j * ks + c] = 0.f;
-                }
+                for (int c = lane; c < d; c += 32) Ks[j * ks + c] = 0.f;
+                for (int c = lane; c < dv; c += 32) Vs[j * vs + c] = 0.f;
             }
         }
         __syncthreads();
@@ -127,7 +131,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
         float pr[RW];
 #pragma unroll
         for (int rr = 0; rr < RW; rr++) {
-            bool valid = row_ok[rr] && key <= row_pos[rr] && (p.window <= 0 || key > row_pos[rr] - p.window);
+            bool valid = row_ok[rr] && key <= row_pos[rr] && (p.window <= 0 || key > row_pos[rr] - p.window || key < p.keep_first);
             float sv = valid ? s[rr] : -INFINITY;
             float m_new = fmaxf(m[rr], warp_max(sv));
             if (m_new == -INFINITY) {
@@ -143,14 +147,14 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
             pr[rr] = pv;
         }
         for (int jj = 0; jj < KT; jj++) {
-            const float* vrow = Vs + jj * ks;
+            const float* vrow = Vs + jj * vs;
 #pragma unroll
             for (int rr = 0; rr < RW; rr++) {
                 float pj = __shfl_sync(0xffffffffu, pr[rr], jj);
 #pragma unroll
                 for (int e = 0; e < NE; e++) {
                     int c = lane + 32 * e;
-                    if (c < d) acc[rr][e] = fmaf(pj, vrow[c], acc[rr][e]);
+                    if (c < dv) acc[rr][e] = fmaf(pj, vrow[c], acc[rr][e]);
                 }
             }
         }
@@ -160,15 +164,22 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
     for (int rr = 0; rr < RW; rr++) {
         if (!row_ok[rr]) continue;
         if (p.num_splits == 1) {
-            T* op = (T*)p.out + (int64_t)(q_start + row_q[rr]) * p.out_row_stride + (int64_t)row_head[rr] * d;
-            float inv = 1.f / l[rr];
+            T* op = (T*)p.out + (int64_t)(q_start + row_q[rr]) * p.out_row_stride + (int64_t)row_head[rr] * dv;
+            float lsum = l[rr], keep = 1.f;
+            if (p.sink) {
+                // one more unit in the denominator: a key of score 0 that has no value
+                const float mf = fmaxf(m[rr], 0.f);
+                keep = expf(m[rr] - mf);
+                lsum = lsum * keep + expf(-mf);
+            }
+            float inv = keep / lsum;
 #pragma unroll
             for (int e = 0; e < NE; e++) {
                 int c = lane + 32 * e;
-                if (c < d) op[c] = from_f32<T>(acc[rr][e] * inv);
+                if (c < dv) op[c] = from_f32<T>(acc[rr][e] * inv);
             }
         } else {
-            float* sp = p.scratch + (((int64_t)seq * p.heads + row_head[rr]) * p.num_splits + split) * (d + 2);
+            float* sp = p.scratch + (((int64_t)seq * p.heads + row_head[rr]) * p.num_splits + split) * (dv + 2);
             if (lane == 0) {
                 sp[0] = m[rr];
                 sp[1] = l[rr];
@@ -176,7 +187,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
 #pragma unroll
             for (int e = 0; e < NE; e++) {
                 int c = lane + 32 * e;
-                if (c < d) sp[2 + c] = acc[rr][e];
+                if (c < dv) sp[2 + c] = acc[rr][e];
             }
         }
     }
@@ -190,7 +201,7 @@ constexpr int MERGE_MAX_SPLITS = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int64_t out_row_stride,
-                                                         const int* __restrict__ seq_q_start, int heads, int d, int num_splits) {
+                                                         const int* __restrict__ seq_q_start, int heads, int d, int num_splits, int sink) {
     __shared__ float w_s[MERGE_MAX_SPLITS];
     __shared__ float l_s;
     pdl_trigger();  // the product that follows may start fetching its weights
@@ -201,6 +212,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
         float M = -INFINITY;
         for (int s = lane; s < num_splits; s += 32) M = fmaxf(M, sp[(int64_t)s * (d + 2)]);
         M = warp_max(M);
+        if (sink) M = fmaxf(M, 0.f);  // the sink's score
         float L = 0.f;
         for (int s = lane; s < num_splits; s += 32) {
             const float ms = sp[(int64_t)s * (d + 2)];
@@ -209,6 +221,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
             L += w * sp[(int64_t)s * (d + 2) + 1];
         }
         L = warp_sum(L);
+        if (sink) L += expf(-M);
         if (lane == 0) l_s = L;
     }
     __syncthreads();
@@ -251,8 +264,9 @@ int launch(const AttnParams& p, cudaStream_t stream) {
     dim3 grid(ceil_div(p.max_q_len, QT), p.kv_heads * hchunks, p.nseq * p.num_splits);
     if (grid.y > 65535 || grid.z > 65535)
         GB_REFUSE("attention_simt: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);
-    size_t smem = ((size_t)ROWS * p.d + 2 * (size_t)KT * (p.d + 1)) * sizeof(float);
-    int ne = ceil_div(p.d, 32);
+    const int dv = p.dv > 0 ? p.dv : p.d;
+    size_t smem = ((size_t)ROWS * p.d + (size_t)KT * (p.d + 1) + (size_t)KT * (dv + 1)) * sizeof(float);
+    int ne = ceil_div(dv, 32);
     int rc;
     switch (ne) {
         case 1: rc = launch_ne<T, 1>(p, grid, smem, stream); break;
@@ -263,12 +277,12 @@ int launch(const AttnParams& p, cudaStream_t stream) {
         case 6: rc = launch_ne<T, 6>(p, grid, smem, stream); break;
         case 7: rc = launch_ne<T, 7>(p, grid, smem, stream); break;
         case 8: rc = launch_ne<T, 8>(p, grid, smem, stream); break;
-        default: GB_REFUSE("attention_simt: head_dim %d is larger than 256", p.d);
+        default: GB_REFUSE("attention_simt: value size %d is larger than 256", dv);
     }
     if (rc) return rc;
     if (p.num_splits > 1) {
         attn_merge_kernel<T><<<dim3(p.heads, p.nseq), 128, 0, stream>>>(p.scratch, (T*)p.out, p.out_row_stride,
-                                                                        p.seq_q_start, p.heads, p.d, p.num_splits);
+                                                                        p.seq_q_start, p.heads, dv, p.num_splits, p.sink);
         GB_CHECK_LAUNCH("attention_merge");
     }
     return 0;
@@ -278,13 +292,13 @@ int launch(const AttnParams& p, cudaStream_t stream) {
 
 // Merge of per-split partial results, shared with the tensor-core single-token kernel.
 int gb_attention_merge_launch(const float* scratch, void* out, int dtype, int64_t out_row_stride, const int* seq_q_start,
-                              int nseq, int heads, int d, int num_splits, cudaStream_t stream) {
+                              int nseq, int heads, int d, int num_splits, int sink, cudaStream_t stream) {
     if (num_splits > MERGE_MAX_SPLITS) GB_REFUSE("attention: %d key splits; at most %d", num_splits, MERGE_MAX_SPLITS);
     if (dtype == GB_F32)
-        attn_merge_kernel<float><<<dim3(heads, nseq), 128, 0, stream>>>(scratch, (float*)out, out_row_stride, seq_q_start, heads, d, num_splits);
+        attn_merge_kernel<float><<<dim3(heads, nseq), 128, 0, stream>>>(scratch, (float*)out, out_row_stride, seq_q_start, heads, d, num_splits, sink);
     else
         attn_merge_kernel<__nv_bfloat16><<<dim3(heads, nseq), 128, 0, stream>>>(scratch, (__nv_bfloat16*)out, out_row_stride,
-                                                                                seq_q_start, heads, d, num_splits);
+                                                                                seq_q_start, heads, d, num_splits, sink);
     GB_CHECK_LAUNCH("attention_merge");
     return 0;
 }
@@ -298,6 +312,8 @@ GB_API int gb_attention_simt(const AttnParams* pp, int dtype, cudaStream_t strea
     if (p.num_splits > 1 && p.max_q_len != 1) GB_REFUSE("attention: key splits need single-token rows, got rows of up to %d", p.max_q_len);
     if (p.num_splits > 1 && !p.scratch) GB_REFUSE("attention: %d key splits without scratch memory", p.num_splits);
     if (p.window < 0) GB_REFUSE("attention: window %d", p.window);
+    if (p.dv < 0 || p.dv > 256) GB_REFUSE("attention_simt: value size %d is outside [1, 256]", p.dv);
+    if (p.keep_first < 0) GB_REFUSE("attention: %d kept first tokens", p.keep_first);
     if (dtype == GB_F32) return launch<float>(p, stream);
     if (dtype == GB_BF16) return launch<__nv_bfloat16>(p, stream);
     GB_REFUSE("attention: unknown dtype %d", dtype);

@@ -557,6 +557,8 @@ GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, c
     if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("%s: %d heads over %d kv heads", who, p.heads, p.kv_heads);
     if (p.num_splits != 1) GB_REFUSE("%s: key splits are for single-token rows", who);
     if (p.window < 0) GB_REFUSE("%s: window %d", who, p.window);
+    if ((p.dv && p.dv != p.d) || p.keep_first || p.sink)
+        GB_REFUSE("%s: values of another size than keys, kept first tokens and a sink run on the CUDA-core kernel", who);
     if (((uintptr_t)p.q & 15) || (p.q_row_stride & 7)) GB_REFUSE("%s: query rows must be 16-byte aligned", who);
     if (((uintptr_t)p.out & 15) || (p.out_row_stride & 7)) GB_REFUSE("%s: output rows must be 16-byte aligned", who);
     if (((uintptr_t)p.k_plane & 15) || ((uintptr_t)p.v_plane & 15)) GB_REFUSE("%s: cache planes must be 16-byte aligned", who);

@@ -47,6 +47,7 @@ SOURCES = [
     "attention_simt.cu",
     "attention_mma.cu",
     "attention_tc5.cu",
+    "linear_state.cu",
     "sampling.cu",
     "no_alloc.cu",
     "dispatch.cu",

@@ -38,7 +38,7 @@ GB_API int gb_is_checked() {
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids, int hidden,
                                     int vocab, float* __restrict__ out, float* __restrict__ stats, int64_t stats_stride,
-                                    const float* __restrict__ next_w, __nv_bfloat16* __restrict__ xn_out, int64_t ldxn) {
+                                    const float* __restrict__ next_w, __nv_bfloat16* __restrict__ xn_out, int64_t ldxn, float scale) {
     __shared__ float warp_part[8];
     int r = blockIdx.x;
     int id = ids[r];
@@ -48,7 +48,7 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     float* dst = out + (int64_t)r * hidden;
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float v = to_f32<T>(src[i]);
+        const float v = to_f32<T>(src[i]) * scale;   // scale 1 changes no bit
         dst[i] = v;
         ss += v * v;
         if (next_w != nullptr) xn_out[(int64_t)r * ldxn + i] = __float2bfloat16_rn(v * next_w[i]);
@@ -67,16 +67,16 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
 
 GB_API int gb_embed_gather(const void* table, int table_dtype, const int* ids, int rows, int hidden, int vocab,
                            float* out, float* stats, int64_t stats_stride, const float* next_w, void* xn_out, int64_t ldxn,
-                           cudaStream_t stream) {
+                           float scale, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) GB_REFUSE("embed_gather: hidden %d, vocab %d", hidden, vocab);
     if (next_w && (!xn_out || ldxn < hidden)) GB_REFUSE("embed_gather: a norm weight is given without room for its %d-wide rows", hidden);
     if (table_dtype == GB_F32)
         embed_gather_kernel<float><<<rows, 256, 0, stream>>>((const float*)table, ids, hidden, vocab, out, stats, stats_stride, next_w,
-                                                             (__nv_bfloat16*)xn_out, ldxn);
+                                                             (__nv_bfloat16*)xn_out, ldxn, scale);
     else if (table_dtype == GB_BF16)
         embed_gather_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, hidden, vocab, out, stats, stats_stride,
-                                                                     next_w, (__nv_bfloat16*)xn_out, ldxn);
+                                                                     next_w, (__nv_bfloat16*)xn_out, ldxn, scale);
     else
         GB_REFUSE("embed_gather: unknown table dtype %d", table_dtype);
     GB_CHECK_LAUNCH("embed_gather");
@@ -343,11 +343,16 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
     int total_heads = p.heads + 2 * p.kv_heads;
     if (head >= total_heads) return;
     int d = p.d;
-    T* src = (T*)p.qkv + (int64_t)r * p.row_stride + (int64_t)head * d;
+    const int dv = p.dv > 0 ? p.dv : d;
     int pos = p.row_pos[r];
     bool is_q = head < p.heads;
     bool is_k = !is_q && head < p.heads + p.kv_heads;
     int kvh = is_q ? 0 : (is_k ? head - p.heads : head - p.heads - p.kv_heads);
+    // q and k heads are d wide, the value heads behind them dv
+    T* src = (T*)p.qkv + (int64_t)r * p.row_stride +
+             (is_q || is_k ? (int64_t)head * d : (int64_t)(p.heads + p.kv_heads) * d + (int64_t)kvh * dv);
+    const float* bias = is_q ? p.q_b : (is_k ? p.k_b : p.v_b);
+    if (bias) bias += (is_q ? head : kvh) * (is_q || is_k ? d : dv);
 
     T* dst = nullptr;
     if (is_q) {
@@ -357,10 +362,13 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
         int slot = p.seq_slot[p.row_seq[r]];
         int64_t page = page_of(block_table_row(p.block_table, p.bt_stride, slot, p.max_slots), pos, p.bt_stride, p.pages);
         T* plane = (T*)(is_k ? p.k_plane : p.v_plane);
-        dst = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos % GB_PAGE)) * (int64_t)d;
+        dst = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos % GB_PAGE)) * (int64_t)(is_k ? d : dv);
     }
-    if (!is_q && !is_k) {  // value head: copy
-        for (int i = lane; i < d; i += 32) dst[i] = src[i];
+    if (!is_q && !is_k) {  // value head: copy (plus its bias)
+        if (bias)
+            for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(to_f32<T>(src[i]) + bias[i]);
+        else
+            for (int i = lane; i < dv; i += 32) dst[i] = src[i];
         return;
     }
     const float* w = is_q ? p.q_w : p.k_w;
@@ -368,6 +376,7 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
     float ss = 0.f;
     for (int i = lane; i < d; i += 32) {
         float v = to_f32<T>(src[i]);
+        if (bias) v += bias[i];
         y[i] = v;
         ss += v * v;
     }
@@ -387,7 +396,15 @@ __global__ void qk_rope_kernel(QkRopeParams p) {
     const float* s = p.sin_t + (int64_t)tpos * half;
     for (int i = lane; i < d; i += 32) {
         float v;
-        if (i < half)
+        if (p.pairs) {
+            // neighbouring channels turn together: (2j, 2j + 1) by angle j
+            if (i < p.rot) {
+                const int j = i >> 1;
+                v = (i & 1) ? y[i] * c[j] + y[i - 1] * s[j] : y[i] * c[j] - y[i + 1] * s[j];
+            } else {
+                v = y[i];
+            }
+        } else if (i < half)
             v = y[i] * c[i] - y[i + half] * s[i];
         else if (i < p.rot)
             v = y[i] * c[i - half] + y[i - half] * s[i - half];
@@ -590,7 +607,9 @@ GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStrea
     if (p.heads <= 0 || p.kv_heads < 0) GB_REFUSE("qk_norm_rope: heads %d, kv heads %d", p.heads, p.kv_heads);
     if (p.rows > 0x7fffffff / 2) GB_REFUSE("qk_norm_rope: %d rows are too many", p.rows);
     int total_heads = p.heads + 2 * p.kv_heads;
-    if (dtype == GB_BF16 && p.d == 128 && p.rot == 128 && !(p.row_stride & 3) && !((uintptr_t)p.qkv & 7) &&
+    if (p.dv < 0 || p.dv > 1024) GB_REFUSE("qk_norm_rope: value size %d is outside [1, 1024]", p.dv);
+    const bool plain = !p.q_b && !p.k_b && !p.v_b && !p.pairs && (p.dv == 0 || p.dv == p.d);
+    if (plain && dtype == GB_BF16 && p.d == 128 && p.rot == 128 && !(p.row_stride & 3) && !((uintptr_t)p.qkv & 7) &&
         !(((uintptr_t)p.q_w | (uintptr_t)p.k_w | (uintptr_t)p.cos_t | (uintptr_t)p.sin_t) & 15) && (p.q_w != nullptr) == (p.k_w != nullptr) &&
         ceil_div(total_heads, 8) <= 65535) {
         // prompts: the kernel of 16-byte accesses (it adds a row's squares up in another order, so a key

@@ -1,0 +1,339 @@
+// Mixers that carry a matrix state per head instead of keys and values: for every token
+//
+//     S <- diag(a_t) S + b_t k_t v_t^T          (S is d x dv, fp32, one per sequence and head)
+//     o_t = S^T q_t
+//
+// with a_t a decay per key channel (gated linear attention) or one number per head (the matrix
+// memory of an mLSTM, where b_t is the input gate and a further column n <- a_t n + b_t k_t gives
+// the normaliser).  State, decays, gates and the sums are fp32 whatever the activation dtype;
+// q, k and v are read as the projection left them.
+//
+// The recurrence runs token by token, in order, for prompts and single tokens alike, so the state
+// after a token is the same bits however the sequence was cut into steps and whatever else the
+// batch holds.  Work is spread over (sequence, head, block of 16 value columns): columns of S are
+// independent of one another.  Inside a CTA a warp owns 4 columns and its 8 groups of lanes own a
+// slice of the key channels each; a thread keeps its d/8 state elements in registers across all
+// tokens of the step, the tokens' q, k and decay rows are staged in shared memory eight tokens at a
+// time, and a token's output is a shuffle sum over the 8 slices.
+#include "api.h"
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+
+constexpr int COLS = 16;     // value columns per CTA
+constexpr int SLICES = 8;    // slices of the key channels
+constexpr int TT = 8;        // tokens staged at a time
+constexpr int THREADS = 128;
+
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+// ------------------------------------------------------------------------------------------
+// decay of gated linear attention, in place: z[r, c] <- sigmoid(z[r, c] + bias[c]) ^ (1 / tau)
+__global__ void gla_decay_kernel(float* __restrict__ z, const float* __restrict__ bias, int64_t total, int width, float inv_tau) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float x = z[i] + (bias ? bias[i % width] : 0.f);
+    z[i] = expf(log_sigmoid(x) * inv_tau);
+}
+
+// ------------------------------------------------------------------------------------------
+// gates of the matrix memory.  One warp per (sequence, head), 32 tokens at a time: the lanes take a
+// token each for the capped gates, the running maximum m_t = max(f_t + m_(t-1), i_t) is walked in
+// order through shuffles (an add and a max a token), then the lanes turn their token's values into
+// the factors keep_t = exp(f_t + m_(t-1) - m_t) and take_t = exp(i_t - m_t).
+// coef[r, h] = (keep, take, m_t, -): the last place is filled by the scan's normaliser column.
+__global__ void __launch_bounds__(32) mlstm_gates_kernel(LinearStateParams p) {
+    const int h = blockIdx.x, seq = blockIdx.y, lane = threadIdx.x;
+    const int q_len = p.seq_q_len[seq], q_start = p.seq_q_start[seq];
+    int slot = p.seq_slot[seq];
+    if (!gb_check(slot, p.max_slots, GB_CHECK_SLOT)) slot = 0;
+    float* m_state = p.state + (int64_t)slot * p.slot_stride + (int64_t)h * p.head_stride + (int64_t)p.d * p.dv + p.d;
+    float m = *m_state;
+    const float cap = p.gate_cap, inv_cap = 1.f / p.gate_cap;
+    const float bi = p.gate_bias ? p.gate_bias[h] : 0.f, bf = p.gate_bias ? p.gate_bias[p.heads + h] : 0.f;
+    for (int t0 = 0; t0 < q_len; t0 += 32) {
+        const int t = t0 + lane;
+        float gi = 0.f, gf = 0.f;
+        if (t < q_len) {
+            const float* g = p.gates + (int64_t)(q_start + t) * p.gates_stride;
+            gi = cap * tanhf((g[h] + bi) * inv_cap);
+            gf = log_sigmoid(cap * tanhf((g[p.heads + h] + bf) * inv_cap));
+        }
+        float m_before = 0.f, m_mine = 0.f;
+        const int n = q_len - t0 < 32 ? q_len - t0 : 32;
+        for (int j = 0; j < n; j++) {
+            const float fj = __shfl_sync(0xffffffffu, gf, j), ij = __shfl_sync(0xffffffffu, gi, j);
+            const float m_new = fmaxf(fj + m, ij);
+            if (lane == j) {
+                m_before = m;
+                m_mine = m_new;
+            }
+            m = m_new;
+        }
+        if (t < q_len) {
+            float4 c;
+            c.x = expf(gf + m_before - m_mine);
+            c.y = expf(gi - m_mine);
+            c.z = m_mine;
+            c.w = 1.f;
+            *reinterpret_cast<float4*>(p.coef + ((int64_t)(q_start + t) * p.heads + h) * 4) = c;
+        }
+    }
+    if (lane == 0) *m_state = m;
+}
+
+// ------------------------------------------------------------------------------------------
+// the scan.  RC: key channels per slice (a multiple of 4, RC * 8 >= d).  SCALAR: one decay per head
+// and token (coef), with the input gate folded into the staged keys and one more block of columns
+// for the normaliser; otherwise a decay per key channel (p.decay).
+template <typename T, int RC, bool SCALAR>
+__global__ void __launch_bounds__(THREADS) state_scan_kernel(LinearStateParams p) {
+    constexpr int P = (RC / 4) % 2 ? RC : RC + 4;   // slice stride in floats: P / 4 odd, so the 8 slices' 16-byte reads miss each other's banks
+    constexpr int ROW = SLICES * P;
+    __shared__ __align__(16) float q_s[TT][ROW];
+    __shared__ __align__(16) float k_s[TT][ROW];
+    __shared__ __align__(16) float a_s[SCALAR ? 1 : TT][SCALAR ? 4 : ROW];
+    __shared__ float v_s[TT][COLS];
+    __shared__ float o_s[TT][COLS];
+    __shared__ float keep_s[TT], m_s[TT];
+    __shared__ float st_s[SLICES * RC][COLS + 1];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int slice = lane & 7, col = warp * 4 + (lane >> 3);   // this thread's slice and column of the CTA's 16
+    const int d = p.d, dv = p.dv, H = p.heads;
+    const int h = blockIdx.y, seq = blockIdx.z;
+    const int vblocks = (dv + COLS - 1) / COLS;
+    const bool norm_col = SCALAR && (int)blockIdx.x == vblocks;   // the block that carries n instead of columns of S
+    const int j0 = blockIdx.x * COLS;
+    const int q_len = p.seq_q_len[seq], q_start = p.seq_q_start[seq];
+    int slot = p.seq_slot[seq];
+    if (!gb_check(slot, p.max_slots, GB_CHECK_SLOT)) slot = 0;
+    float* S = p.state + (int64_t)slot * p.slot_stride + (int64_t)h * p.head_stride;
+    float* nvec = S + (int64_t)d * dv;
+
+    // the state block of this CTA, through shared memory so that global rows are read whole
+    for (int idx = tid; idx < SLICES * RC * COLS; idx += THREADS) {
+        const int c = idx / COLS, jj = idx % COLS;
+        float v = 0.f;
+        if (c < d) {
+            if (norm_col)
+                v = jj == 0 ? nvec[c] : 0.f;
+            else if (j0 + jj < dv)
+                v = S[(int64_t)c * dv + j0 + jj];
+        }
+        st_s[c][jj] = v;
+    }
+    __syncthreads();
+    float st[RC];
+#pragma unroll
+    for (int i = 0; i < RC; i++) st[i] = st_s[slice * RC + i][col];
+
+    const T* base = (const T*)p.qkv;
+    for (int t0 = 0; t0 < q_len; t0 += TT) {
+        const int nt = q_len - t0 < TT ? q_len - t0 : TT;
+        __syncthreads();   // the tile before is done with
+        // stage the tokens' rows: q scaled, k (times the input gate), the decays, this block's values
+        for (int idx = tid; idx < nt * SLICES * RC; idx += THREADS) {
+            const int t = idx / (SLICES * RC), c = idx % (SLICES * RC);
+            const int64_t row = q_start + t0 + t;
+            const int at = (c / RC) * P + c % RC;
+            float qv = 0.f, kv = 0.f, av = 0.f;
+            if (c < d) {
+                const T* r = base + row * p.row_stride;
+                qv = to_f32<T>(r[p.q_off + h * d + c]) * p.q_scale;
+                kv = to_f32<T>(r[p.k_off + h * d + c]);
+                if (SCALAR)
+                    kv *= p.coef[(row * H + h) * 4 + 1];
+                else
+                    av = p.decay[row * p.decay_stride + h * d + c];
+            }
+            q_s[t][at] = qv;
+            k_s[t][at] = kv;
+            if (!SCALAR) a_s[t][at] = av;
+        }
+        for (int idx = tid; idx < nt * COLS; idx += THREADS) {
+            const int t = idx / COLS, jj = idx % COLS;
+            const int64_t row = q_start + t0 + t;
+            float v = 0.f;
+            if (norm_col)
+                v = jj == 0 ? 1.f : 0.f;
+            else if (j0 + jj < dv)
+                v = to_f32<T>(base[row * p.row_stride + p.v_off + h * dv + j0 + jj]);
+            v_s[t][jj] = v;
+        }
+        if (SCALAR && tid < nt) {
+            const int64_t row = q_start + t0 + tid;
+            keep_s[tid] = p.coef[(row * H + h) * 4];
+            m_s[tid] = p.coef[(row * H + h) * 4 + 2];
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; t++) {
+            const float vj = v_s[t][col];
+            const float keep = SCALAR ? keep_s[t] : 0.f;
+            float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < RC; i += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(&q_s[t][slice * P + i]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&k_s[t][slice * P + i]);
+                float4 a4 = make_float4(keep, keep, keep, keep);
+                if (!SCALAR) a4 = *reinterpret_cast<const float4*>(&a_s[t][slice * P + i]);
+                st[i] = fmaf(a4.x, st[i], k4.x * vj);
+                st[i + 1] = fmaf(a4.y, st[i + 1], k4.y * vj);
+                st[i + 2] = fmaf(a4.z, st[i + 2], k4.z * vj);
+                st[i + 3] = fmaf(a4.w, st[i + 3], k4.w * vj);
+                acc0 = fmaf(st[i], q4.x, acc0);
+                acc1 = fmaf(st[i + 1], q4.y, acc1);
+                acc2 = fmaf(st[i + 2], q4.z, acc2);
+                acc3 = fmaf(st[i + 3], q4.w, acc3);
+            }
+            float acc = (acc0 + acc1) + (acc2 + acc3);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            if (slice == 0) o_s[t][col] = acc;
+        }
+        __syncthreads();
+        if (norm_col) {
+            // n . q of the tile's tokens -> the divisor max(|n . q|, exp(-m)) + 1e-6
+            if (tid < nt) {
+                const int64_t row = q_start + t0 + tid;
+                p.coef[(row * H + h) * 4 + 3] = fmaxf(fabsf(o_s[tid][0]), expf(-m_s[tid])) + 1e-6f;
+            }
+        } else {
+            for (int idx = tid; idx < nt * COLS; idx += THREADS) {
+                const int t = idx / COLS, jj = idx % COLS;
+                if (j0 + jj < dv) p.out[(int64_t)(q_start + t0 + t) * p.out_stride + h * dv + j0 + jj] = o_s[t][jj];
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RC; i++) st_s[slice * RC + i][col] = st[i];
+    __syncthreads();
+    for (int idx = tid; idx < SLICES * RC * COLS; idx += THREADS) {
+        const int c = idx / COLS, jj = idx % COLS;
+        if (c >= d) continue;
+        if (norm_col) {
+            if (jj == 0) nvec[c] = st_s[c][0];
+        } else if (j0 + jj < dv) {
+            S[(int64_t)c * dv + j0 + jj] = st_s[c][jj];
+        }
+    }
+}
+
+template <typename T, bool SCALAR>
+int launch_scan(const LinearStateParams& p, cudaStream_t stream) {
+    const int rc = ((p.d + SLICES - 1) / SLICES + 3) / 4 * 4;
+    dim3 grid((p.dv + COLS - 1) / COLS + (SCALAR ? 1 : 0), p.heads, p.nseq);
+    if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("state_scan: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);
+    switch (rc) {
+        case 4: state_scan_kernel<T, 4, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;
+        case 8: state_scan_kernel<T, 8, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;
+        case 12: state_scan_kernel<T, 12, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;
+        case 16: state_scan_kernel<T, 16, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;
+        case 20: state_scan_kernel<T, 20, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;
+        case 24: state_scan_kernel<T, 24, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;
+        case 28: state_scan_kernel<T, 28, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;
+        case 32: state_scan_kernel<T, 32, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;
+        default: GB_REFUSE("state_scan: %d key channels a head; at most 256", p.d);
+    }
+    GB_CHECK_LAUNCH("state_scan");
+    return 0;
+}
+
+int check(const LinearStateParams& p, const char* who) {
+    if (p.heads <= 0 || p.d <= 0 || p.d > 256 || p.dv <= 0) GB_REFUSE("%s: %d heads of %d key and %d value channels", who, p.heads, p.d, p.dv);
+    if (!p.qkv || !p.state || !p.out) GB_REFUSE("%s: a tensor is missing", who);
+    if (p.head_stride < (int64_t)p.d * p.dv || p.slot_stride < p.head_stride * p.heads) GB_REFUSE("%s: the state is too small for its heads", who);
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// per (row, head): y = norm(x / div) * w * gate(g), everything optional but the gate.  One warp a head.
+template <typename TI, typename T>
+__global__ void __launch_bounds__(128) head_norm_gate_kernel(HeadGateParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r = blockIdx.x;
+    const int h = blockIdx.y * 4 + warp;
+    if (h >= p.heads) return;
+    const int n = p.size;
+    const TI* x = (const TI*)p.x + r * p.x_stride + (int64_t)h * n;
+    const T* g = (const T*)p.gate + r * p.gate_stride + (int64_t)h * n;
+    T* y = (T*)p.y + r * p.y_stride + (int64_t)h * n;
+    const float div = p.divisor ? p.divisor[(r * p.heads + h) * p.divisor_stride] : 1.f;
+    float ss = 0.f;
+    if (p.normed) {
+        for (int i = lane; i < n; i += 32) {
+            const float v = to_f32<TI>(x[i]) / div;
+            ss += v * v;
+        }
+        ss = warp_sum(ss);
+    }
+    const float inv = p.normed ? 1.0f / sqrtf(ss / (float)n + p.eps) : 1.f;
+    const float* w = p.weight ? p.weight + (p.weight_per_head ? (int64_t)h * n : 0) : nullptr;
+    for (int i = lane; i < n; i += 32) {
+        float v = to_f32<TI>(x[i]);
+        if (p.divisor) v /= div;
+        if (p.normed) v *= inv;
+        if (w) v *= w[i];
+        const float z = to_f32<T>(g[i]);
+        const float s = 1.f / (1.f + expf(-z));
+        v *= p.gate_kind == 1 ? z * s : s;
+        y[i] = from_f32<T>(v);
+    }
+}
+
+template <typename TI, typename T>
+int launch_gate(const HeadGateParams& p, cudaStream_t stream) {
+    dim3 grid(p.rows, (p.heads + 3) / 4);
+    if (grid.y > 65535) GB_REFUSE("head_norm_gate: %d heads exceed one launch", p.heads);
+    head_norm_gate_kernel<TI, T><<<grid, 128, 0, stream>>>(p);
+    GB_CHECK_LAUNCH("head_norm_gate");
+    return 0;
+}
+
+}  // namespace
+
+GB_API int gb_gla_decay(float* z, const float* bias, int rows, int width, float tau, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0 || !(tau > 0.f)) GB_REFUSE("gla_decay: width %d, tau %g", width, (double)tau);
+    const int64_t total = (int64_t)rows * width;
+    gla_decay_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(z, bias, total, width, 1.f / tau);
+    GB_CHECK_LAUNCH("gla_decay");
+    return 0;
+}
+
+GB_API int gb_state_scan(const LinearStateParams* pp, int dtype, cudaStream_t stream) {
+    LinearStateParams p = *pp;
+    if (p.nseq <= 0) return 0;
+    if (int rc = check(p, "state_scan")) return rc;
+    if (p.scalar_decay) {
+        if (!p.coef || !p.gates || !(p.gate_cap > 0.f)) GB_REFUSE("state_scan: gates, their cap (%g) or room for the factors is missing", (double)p.gate_cap);
+        if (p.head_stride < (int64_t)p.d * p.dv + p.d + 1) GB_REFUSE("state_scan: the state has no room for the normaliser and the maximum");
+        mlstm_gates_kernel<<<dim3(p.heads, p.nseq), 32, 0, stream>>>(p);
+        GB_CHECK_LAUNCH("mlstm_gates");
+        if (dtype == GB_F32) return launch_scan<float, true>(p, stream);
+        if (dtype == GB_BF16) return launch_scan<__nv_bfloat16, true>(p, stream);
+    } else {
+        if (!p.decay) GB_REFUSE("state_scan: no decays");
+        if (dtype == GB_F32) return launch_scan<float, false>(p, stream);
+        if (dtype == GB_BF16) return launch_scan<__nv_bfloat16, false>(p, stream);
+    }
+    GB_REFUSE("state_scan: unknown dtype %d", dtype);
+}
+
+GB_API int gb_head_norm_gate(const HeadGateParams* pp, int x_dtype, int dtype, cudaStream_t stream) {
+    HeadGateParams p = *pp;
+    if (p.rows <= 0) return 0;
+    if (p.heads <= 0 || p.size <= 0) GB_REFUSE("head_norm_gate: %d heads of %d", p.heads, p.size);
+    if (p.gate_kind != 0 && p.gate_kind != 1) GB_REFUSE("head_norm_gate: gate kind %d", p.gate_kind);
+    if (dtype == GB_F32 && x_dtype == GB_F32) return launch_gate<float, float>(p, stream);
+    if (dtype == GB_BF16 && x_dtype == GB_F32) return launch_gate<float, __nv_bfloat16>(p, stream);
+    if (dtype == GB_BF16 && x_dtype == GB_BF16) return launch_gate<__nv_bfloat16, __nv_bfloat16>(p, stream);
+    GB_REFUSE("head_norm_gate: input dtype %d with output dtype %d", x_dtype, dtype);
+}
+
+// the checked build's record of the first index this file's kernels found out of bounds
+GB_CHECK_READER(gb_checked_status_linear_state)

@@ -18,6 +18,7 @@ from .. import registry
 from ..cache import Cache
 from ..parts.base import RowStats, Runtime, fold_buffers, fold_weight
 from ..weights import InitScales, declare_model, load_tensors, random_tensors_on_device
+from ..weights.declare import final_norm_prefix
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            "f32": torch.float32}
@@ -54,7 +55,7 @@ class Model:
                        for layer in spec.layers]
         # a block arrangement may take the norm that follows it (to prepare the residual's rows for it)
         self._takes_next_norm = ["next_norm" in inspect.signature(b.forward).parameters for b in self.blocks]
-        norm_prefix = spec.final_norm_name[:-len("weight")]
+        norm_prefix = final_norm_prefix(spec)
         self.final_norm = registry.part_class("norm", spec.final_norm.kind)(spec.final_norm, norm_prefix, tensors, runtime)
         if spec.head.name in tensors:
             self.head = tensors[spec.head.name]
@@ -139,6 +140,7 @@ class Model:
         # What is still owed to the residual travels from block to block: an addend not yet added, the
         # rows' statistics (``RowStats``) where the last kernel left them, or nothing.
         pending = None
+        scale = float(getattr(self.spec.embedding, "scale", 1.0))
         schedule = self.spec.schedule
         first = self.blocks[schedule[0].layer]
         weight = None
@@ -150,10 +152,10 @@ class Model:
             weight = fold_weight(first.first_norm(), self.spec.hidden)
         if weight is not None:
             stats, prescaled = fold_buffers(batch, 0, self.spec.hidden)
-            ops.embed_gather(self.embedding, batch.ids, h, stats, weight, prescaled[:rows])
+            ops.embed_gather(self.embedding, batch.ids, h, stats, weight, prescaled[:rows], scale=scale)
             pending = RowStats(stats, 1, prescaled[:rows], first.first_norm())
         else:
-            ops.embed_gather(self.embedding, batch.ids, h)
+            ops.embed_gather(self.embedding, batch.ids, h, scale=scale)
         for pos, entry in enumerate(schedule):
             block = self.blocks[entry.layer]
             if self._takes_next_norm[entry.layer]:

@@ -378,7 +378,14 @@ class Engine:
             if source is not None:
                 self.model.rt.ops.gather_tokens(g.meta[:n], source)
             torch.cuda.synchronize()
+            # The capture runs the step once for real before it records it, and the replay below runs it
+            # again.  Keys and values land where they landed before; a mixer's fixed-size state would
+            # have moved on twice, so it is put back.
+            slots = [slot for slot, _ in entries] + [self.cache.spare_slot]
+            saved = [self.cache.copy_state(slot) for slot in slots] if self.cache.has_state() else []
             g.capture()
+            for slot, state in zip(slots, saved):
+                self.cache.put_state(slot, state)
         self._fill_graph_meta(g, entries, firsts)
         if source is not None:
             self.model.rt.ops.gather_tokens(g.meta[:n], source)  # the ids section held positions

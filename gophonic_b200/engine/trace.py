@@ -28,7 +28,7 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at once, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at once")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -38,7 +38,9 @@ def main(argv=None) -> int:
 
     os.makedirs(args.out, exist_ok=True)
     model = Model.from_dir(args.model, dtype=args.dtype, device=args.device)
-    engine = Engine(model, max_tokens=args.max_tokens)
+    # the cache hands out pages of 64 tokens and a request's last page is rarely full: room for that
+    # slack, one page for each request that could be live at once
+    engine = Engine(model, max_tokens=args.max_tokens + 64 * min(max(args.max_tokens, 1), 256))
     slots: Dict[str, int] = {}
 
     for line in sys.stdin:

@@ -89,8 +89,8 @@ def _need(t: torch.Tensor, name: str, dtype=None, dim=None, contiguous=True) -> 
 
 # ---- embedding ---------------------------------------------------------------------------
 def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stats: Optional[torch.Tensor] = None,
-                 next_weight: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None) -> None:
-    """out[r, :] = float32(table[ids[r], :]).  With ``stats`` (float32 [>= rows, capacity]) the sum of
+                 next_weight: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """out[r, :] = float32(table[ids[r], :]) * scale (one float32 multiplication; 1 changes no bit).  With ``stats`` (float32 [>= rows, capacity]) the sum of
     squares of row r is left in stats[r, 0]: one partial sum a row.  With ``next_weight`` (float32
     [hidden]) and ``next_x`` (bfloat16 [rows, hidden]) also next_x = bf16(out * next_weight): the
     output of an RMSNorm with that weight but for each row's factor."""
@@ -109,7 +109,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
     ldxn = _check_next(next_weight, next_x, rows, hidden, "embed_gather")
     _check(_lib.gb_embed_gather(_ptr(table), _code(table.dtype), _ptr(ids), c_int(rows), c_int(hidden),
                                 c_int(table.shape[0]), _ptr(out), _ptr(stats), c_int64(stride), _ptr(next_weight), _ptr(next_x),
-                                c_int64(ldxn), _stream()))
+                                c_int64(ldxn), c_float(scale), _stream()))
 
 
 def _check_next(next_weight, next_x, rows: int, width: int, who: str) -> int:
@@ -471,7 +471,7 @@ def checked_status():
     found out of bounds since the last call (the access was skipped or redirected, nothing faulted).
     Always None in the ordinary build, whose kernels carry no checks.  Synchronises."""
     out = (c_int * 4)()
-    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5"):
+    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5", "linear_state"):
         code = int(getattr(_lib, "gb_checked_status_" + name)(out))
         if code or out[3]:
             return name, _CHECK_NAMES.get(code, f"code {code}"), out[1], out[2], out[3]
@@ -495,6 +495,7 @@ class _QkRopeParams(Structure):
         ("bt_stride", c_int), ("k_plane", c_void_p), ("v_plane", c_void_p),
         ("write_kv", c_int), ("rows", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
         ("pages", c_int), ("max_slots", c_int),
+        ("q_b", c_void_p), ("k_b", c_void_p), ("v_b", c_void_p), ("pairs", c_int), ("dv", c_int),
     ]
 
 
@@ -503,11 +504,25 @@ def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                  cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int,
                  row_pos: torch.Tensor, row_seq: torch.Tensor, seq_slot: torch.Tensor,
                  block_table: torch.Tensor,
-                 k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], write_kv: bool) -> "_QkRopeParams":
-    _need(qkv, "qkv", dim=2)
+                 k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], write_kv: bool,
+                 biases=None, pairs: bool = False, value_dim: Optional[int] = None) -> "_QkRopeParams":
+    """``biases`` = (q, k, v) float32 vectors or None each, added to the heads first; ``pairs``: channels
+    2j and 2j + 1 turn together instead of j and j + rotary_dim / 2; ``value_dim``: size of a value
+    head if it is not ``head_dim``.  With any of them the rows may be wider than q, k and v (what
+    follows them is left alone)."""
+    _need(qkv, "qkv", dim=2, contiguous=False)
     rows = qkv.shape[0]
-    if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
-        raise KernelError(f"qk_norm_rope: qkv {tuple(qkv.shape)} for {heads}+2x{kv_heads} heads of {head_dim}")
+    dv = head_dim if value_dim is None else int(value_dim)
+    general = biases is not None or pairs or dv != head_dim
+    used = (heads + kv_heads) * head_dim + kv_heads * dv
+    if qkv.stride(1) != 1 or (qkv.shape[1] < used if general else (qkv.shape[1] != used or not qkv.is_contiguous())):
+        raise KernelError(f"qk_norm_rope: qkv {tuple(qkv.shape)} for {heads}+{kv_heads} heads of {head_dim} and {kv_heads} of {dv}")
+    q_b, k_b, v_b = biases if biases is not None else (None, None, None)
+    for t, nm, n in ((q_b, "q bias", heads * head_dim), (k_b, "k bias", kv_heads * head_dim), (v_b, "v bias", kv_heads * dv)):
+        if t is not None:
+            _need(t, nm, torch.float32, 1)
+            if t.numel() != n:
+                raise KernelError(f"qk_norm_rope: {nm} has {t.numel()} elements, want {n}")
     for t, nm in ((q_weight, "q norm"), (k_weight, "k norm")):
         if t is not None:
             _need(t, nm, torch.float32, 1)
@@ -524,10 +539,10 @@ def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
         _need(t, nm, torch.int32, 1)
     _need(block_table, "block table", torch.int32, 2)
     if write_kv:
-        for t, nm in ((k_plane, "key plane"), (v_plane, "value plane")):
+        for t, nm, n in ((k_plane, "key plane", head_dim), (v_plane, "value plane", dv)):
             _need(t, nm, qkv.dtype, 4)
-            if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != head_dim:
-                raise KernelError(f"qk_norm_rope: {nm} {tuple(t.shape)} for {kv_heads} kv heads of {head_dim}")
+            if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != n:
+                raise KernelError(f"qk_norm_rope: {nm} {tuple(t.shape)} for {kv_heads} kv heads of {n}")
     p = _QkRopeParams(qkv.data_ptr(), qkv.stride(0), 0 if q_weight is None else q_weight.data_ptr(),
                       0 if k_weight is None else k_weight.data_ptr(), eps,
                       0 if cos is None else cos.data_ptr(), 0 if sin is None else sin.data_ptr(), rotary_dim,
@@ -535,15 +550,18 @@ def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                       block_table.data_ptr(), block_table.stride(0),
                       0 if k_plane is None else k_plane.data_ptr(), 0 if v_plane is None else v_plane.data_ptr(),
                       1 if write_kv else 0, rows, heads, kv_heads, head_dim,
-                      0 if k_plane is None else k_plane.shape[0], block_table.shape[0])
+                      0 if k_plane is None else k_plane.shape[0], block_table.shape[0],
+                      0 if q_b is None else q_b.data_ptr(), 0 if k_b is None else k_b.data_ptr(),
+                      0 if v_b is None else v_b.data_ptr(), 1 if pairs else 0, dv)
     return p
 
 
-def qk_norm_rope_kv_write(qkv: torch.Tensor, *args) -> None:
-    """Per-head RMSNorm of q and k, rotary embedding of both, q in place, k and v into the cache:
-    (qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps, cos, sin, rotary_dim, row_pos, row_seq,
-    seq_slot, block_table, k_plane, v_plane, write_kv)."""
-    p = _rope_params(qkv, *args)
+def qk_norm_rope_kv_write(qkv: torch.Tensor, *args, **kwargs) -> None:
+    """Biases (optional), per-head RMSNorm of q and k (optional), rotary embedding of both, q in place,
+    k and v into the cache: (qkv, heads, kv_heads, head_dim, q_weight, k_weight, eps, cos, sin,
+    rotary_dim, row_pos, row_seq, seq_slot, block_table, k_plane, v_plane, write_kv) and the keywords
+    of ``_rope_params``."""
+    p = _rope_params(qkv, *args, **kwargs)
     _check(_lib.gb_qk_norm_rope_kv_write(byref(p), _code(qkv.dtype), _stream()))
 
 
@@ -554,7 +572,7 @@ class _AttnParams(Structure):
         ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
         ("seq_kv_len", c_void_p), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
         ("max_q_len", c_int), ("scale", c_float), ("window", c_int), ("num_splits", c_int), ("scratch", c_void_p),
-        ("pages", c_int), ("max_slots", c_int),
+        ("pages", c_int), ("max_slots", c_int), ("dv", c_int), ("keep_first", c_int), ("sink", c_int),
     ]
 
 
@@ -566,15 +584,21 @@ def _attn_params(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_pl
                  block_table: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
                  seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
                  heads: int, kv_heads: int, head_dim: int, scale: float, window: int,
-                 num_splits: int, scratch: Optional[torch.Tensor]) -> "_AttnParams":
+                 num_splits: int, scratch: Optional[torch.Tensor], value_dim: Optional[int] = None, keep_first: int = 0,
+                 sink: bool = False) -> "_AttnParams":
+    """``value_dim``: size of a value head if it is not ``head_dim``; ``keep_first``: with a window, keys
+    at positions below it stay visible; ``sink``: one more unit in the softmax denominator."""
     _need(q, "attention q", dim=2, contiguous=False)
     _need(out, "attention out", q.dtype, 2, contiguous=False)
-    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] < heads * head_dim or out.shape[1] < heads * head_dim:
-        raise KernelError(f"attention: q {tuple(q.shape)}, out {tuple(out.shape)} for {heads} heads of {head_dim}")
-    for t, nm in ((k_plane, "key plane"), (v_plane, "value plane")):
+    dv = head_dim if value_dim is None else int(value_dim)
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.shape[1] < heads * head_dim or out.shape[1] < heads * dv:
+        raise KernelError(f"attention: q {tuple(q.shape)}, out {tuple(out.shape)} for {heads} heads of {head_dim} / {dv}")
+    if keep_first < 0:
+        raise KernelError(f"attention: {keep_first} kept first tokens")
+    for t, nm, n in ((k_plane, "key plane", head_dim), (v_plane, "value plane", dv)):
         _need(t, nm, q.dtype, 4)
-        if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != head_dim:
-            raise KernelError(f"attention: {nm} {tuple(t.shape)} for {kv_heads} kv heads of {head_dim}")
+        if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != n:
+            raise KernelError(f"attention: {nm} {tuple(t.shape)} for {kv_heads} kv heads of {n}")
     for t, nm in ((seq_slot, "seq_slot"), (seq_q_start, "seq_q_start"), (seq_q_len, "seq_q_len"),
                   (seq_kv_len, "seq_kv_len")):
         _need(t, nm, torch.int32, 1)
@@ -585,13 +609,14 @@ def _attn_params(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_pl
         if scratch is None:
             raise KernelError("attention: key splits need scratch memory")
         _need(scratch, "attention scratch", torch.float32)
-        if scratch.numel() < attention_scratch_floats(nseq, heads, head_dim, num_splits):
+        if scratch.numel() < attention_scratch_floats(nseq, heads, dv, num_splits):
             raise KernelError("attention: scratch is too small")
     p = _AttnParams(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_plane.data_ptr(), v_plane.data_ptr(),
                     block_table.data_ptr(), block_table.stride(0), seq_slot.data_ptr(),
                     seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_kv_len.data_ptr(), nseq, heads, kv_heads,
                     head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr(),
-                    k_plane.shape[0], block_table.shape[0])
+                    k_plane.shape[0], block_table.shape[0], 0 if dv == head_dim else dv, int(keep_first) if window > 0 else 0,
+                    1 if sink else 0)
     return p
 
 
@@ -599,11 +624,12 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
               block_table: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
               seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
               heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
-              num_splits: int = 1, scratch: Optional[torch.Tensor] = None, algo: str = "auto") -> str:
+              num_splits: int = 1, scratch: Optional[torch.Tensor] = None, algo: str = "auto",
+              value_dim: Optional[int] = None, keep_first: int = 0, sink: bool = False) -> str:
     """Causal GQA over the paged cache.  q is a [rows, >= heads*head_dim] view (row stride free),
-    out is [rows, heads*head_dim].  Returns the kernel's name."""
+    out is [rows, heads*value_dim].  Returns the kernel's name."""
     p = _attn_params(q, out, k_plane, v_plane, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len, nseq, max_q_len,
-                     heads, kv_heads, head_dim, scale, window, num_splits, scratch)
+                     heads, kv_heads, head_dim, scale, window, num_splits, scratch, value_dim, keep_first, sink)
     if algo == "auto":   # the library's own rule (head size, rows per sequence, alignment)
         algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5")[int(_lib.gb_attention_algo(byref(p), _code(q.dtype)))]
     nk = 2 if num_splits > 1 else 1
@@ -634,6 +660,120 @@ def attention_decode_rope(qkv: torch.Tensor, out: torch.Tensor, rope_args: tuple
     r = _rope_params(qkv, *rope_args)
     a = _attn_params(qkv[:, :r.heads * r.d], out, *attn_args)
     _check(_lib.gb_attention_decode_mma_rope(byref(a), byref(r), _stream()), 2 if a.num_splits > 1 else 1)
+
+
+# ---- mixers with a matrix state ------------------------------------------------------------
+class _LinearStateParams(Structure):
+    _fields_ = [
+        ("qkv", c_void_p), ("row_stride", c_int64), ("q_off", c_int), ("k_off", c_int), ("v_off", c_int), ("q_scale", c_float),
+        ("decay", c_void_p), ("decay_stride", c_int64), ("gates", c_void_p), ("gates_stride", c_int64), ("gate_bias", c_void_p),
+        ("gate_cap", c_float), ("coef", c_void_p), ("state", c_void_p), ("slot_stride", c_int64), ("head_stride", c_int64),
+        ("out", c_void_p), ("out_stride", c_int64), ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
+        ("nseq", c_int), ("heads", c_int), ("d", c_int), ("dv", c_int), ("scalar_decay", c_int), ("max_slots", c_int),
+    ]
+
+
+class _HeadGateParams(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("x_stride", c_int64), ("gate", c_void_p), ("gate_stride", c_int64), ("y", c_void_p), ("y_stride", c_int64),
+        ("divisor", c_void_p), ("divisor_stride", c_int), ("weight", c_void_p), ("weight_per_head", c_int), ("normed", c_int),
+        ("eps", c_float), ("gate_kind", c_int), ("rows", c_int), ("heads", c_int), ("size", c_int),
+    ]
+
+
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
+def gla_decay(z: torch.Tensor, bias: Optional[torch.Tensor], tau: float) -> None:
+    """In place: z[r, c] = sigmoid(z[r, c] + bias[c]) ** (1 / tau), float32."""
+    _need(z, "decay pre-activations", torch.float32, 2)
+    if bias is not None:
+        _need(bias, "decay bias", torch.float32, 1)
+        if bias.numel() != z.shape[1]:
+            raise KernelError(f"gla_decay: bias of {bias.numel()} for rows of {z.shape[1]}")
+    _check(_lib.gb_gla_decay(_ptr(z), _ptr(bias), c_int(z.shape[0]), c_int(z.shape[1]), c_float(tau), _stream()))
+
+
+def state_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, d: int, dv: int, q_scale: float,
+               state: torch.Tensor, out: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor,
+               nseq: int, decay: Optional[torch.Tensor] = None, gates: Optional[torch.Tensor] = None,
+               gate_bias: Optional[torch.Tensor] = None, gate_cap: float = 0.0, coef: Optional[torch.Tensor] = None) -> None:
+    """The matrix-state recurrence S <- diag(a) S + b k v^T, o = S^T (q * q_scale) over the rows of a step,
+    token by token, for every (sequence, head); ``state`` [slots, heads, d * dv (+ d + 1)] float32 is read
+    and left updated, ``out`` [rows, heads * dv] float32 receives the sums.  With ``decay`` (float32 [rows,
+    heads * d]) a is a factor per key channel and b = 1.  With ``gates`` (float32 [rows, 2 * heads]: input
+    then forget pre-activations), ``gate_bias``, ``gate_cap`` and ``coef`` (float32 [rows, heads, 4] scratch)
+    a and b are the stabilised exponential gates of a matrix memory, the state also carries the
+    normaliser and the running maximum, and coef[..., 3] receives each token's divisor."""
+    _need(qkv, "state_scan rows", dim=2, contiguous=False)
+    _need(state, "state", torch.float32, 3)
+    _need(out, "state_scan out", torch.float32, 2)
+    rows = qkv.shape[0]
+    scalar = gates is not None
+    need = d * dv + (d + 1 if scalar else 0)
+    if (qkv.stride(1) != 1 or out.shape != (rows, heads * dv) or state.shape[1] != heads or state.shape[2] < need
+            or max(q_off, k_off) + heads * d > qkv.shape[1] or v_off + heads * dv > qkv.shape[1]):
+        raise KernelError(f"state_scan: rows {tuple(qkv.shape)}, state {tuple(state.shape)}, out {tuple(out.shape)} for "
+                          f"{heads} heads of {d} x {dv}")
+    for t, nm in ((seq_slot, "seq_slot"), (seq_q_start, "seq_q_start"), (seq_q_len, "seq_q_len")):
+        _need(t, nm, torch.int32, 1)
+        if t.numel() < nseq:
+            raise KernelError(f"state_scan: {nm} has {t.numel()} entries for {nseq} sequences")
+    if scalar:
+        _need(gates, "gates", torch.float32, 2, contiguous=False)
+        _need(coef, "gate factors", torch.float32, 3)
+        if gates.shape != (rows, 2 * heads) or gates.stride(1) != 1 or coef.shape[0] < rows or coef.shape[1:] != (heads, 4):
+            raise KernelError(f"state_scan: gates {tuple(gates.shape)}, factors {tuple(coef.shape)}")
+        if gate_bias is not None:
+            _need(gate_bias, "gate bias", torch.float32, 1)
+            if gate_bias.numel() != 2 * heads:
+                raise KernelError(f"state_scan: gate bias of {gate_bias.numel()} for {heads} heads")
+    else:
+        if decay is None:
+            raise KernelError("state_scan: neither decays nor gates")
+        _need(decay, "decays", torch.float32, 2, contiguous=False)
+        if decay.shape != (rows, heads * d) or decay.stride(1) != 1:
+            raise KernelError(f"state_scan: decays {tuple(decay.shape)} for {heads} heads of {d}")
+    p = _LinearStateParams(qkv.data_ptr(), qkv.stride(0), q_off, k_off, v_off, q_scale,
+                           0 if decay is None else decay.data_ptr(), 0 if decay is None else decay.stride(0),
+                           0 if gates is None else gates.data_ptr(), 0 if gates is None else gates.stride(0),
+                           0 if gate_bias is None else gate_bias.data_ptr(), gate_cap, 0 if coef is None else coef.data_ptr(),
+                           state.data_ptr(), state.stride(0), state.stride(1), out.data_ptr(), out.stride(0),
+                           seq_slot.data_ptr(), seq_q_start.data_ptr(), seq_q_len.data_ptr(), nseq, heads, d, dv,
+                           1 if scalar else 0, state.shape[0])
+    _check(_lib.gb_state_scan(byref(p), _code(qkv.dtype), _stream()), 2 if scalar else 1)
+
+
+def head_norm_gate(x: torch.Tensor, gate: torch.Tensor, y: torch.Tensor, heads: int, size: int, gate_kind: int,
+                   weight: Optional[torch.Tensor] = None, eps: Optional[float] = None, divisor: Optional[torch.Tensor] = None) -> None:
+    """y[r, h] = norm(x[r, h] / divisor[r, h]) * weight * gate(g[r, h]) for heads of ``size``: the division
+    only with ``divisor`` (float32 [rows, heads, 1], possibly a column of a wider tensor), the norm (x over its root mean
+    square, eps under the root) only with ``eps``, the weight ([size], shared by the heads, or
+    [heads * size]) only if given; the gate is sigmoid(g) or, with ``GATE_SILU``, g * sigmoid(g).
+    x is float32 or the activation dtype; g and y are the activation dtype; all arithmetic float32."""
+    _need(x, "head_norm_gate x", dim=2, contiguous=False)
+    _need(gate, "head_norm_gate gate", y.dtype, 2, contiguous=False)
+    _need(y, "head_norm_gate y", dim=2, contiguous=False)
+    rows = x.shape[0]
+    n = heads * size
+    if (x.shape[1] < n or gate.shape != (rows, n) or y.shape != (rows, n) or x.stride(1) != 1 or gate.stride(1) != 1 or y.stride(1) != 1):
+        raise KernelError(f"head_norm_gate: x {tuple(x.shape)}, gate {tuple(gate.shape)}, y {tuple(y.shape)} for {heads} heads of {size}")
+    per_head = 0
+    if weight is not None:
+        _need(weight, "head norm weight", torch.float32, 1)
+        if weight.numel() not in (size, n):
+            raise KernelError(f"head_norm_gate: weight of {weight.numel()} for {heads} heads of {size}")
+        per_head = 1 if weight.numel() == n and heads > 1 else 0
+    dstride = 0
+    if divisor is not None:
+        _need(divisor, "divisor", torch.float32, 3, contiguous=False)
+        dstride = divisor.stride(1)
+        if divisor.shape[0] < rows or divisor.shape[1] != heads or divisor.stride(0) != heads * dstride:
+            raise KernelError(f"head_norm_gate: divisor {tuple(divisor.shape)} with strides {divisor.stride()}")
+    p = _HeadGateParams(x.data_ptr(), x.stride(0), gate.data_ptr(), gate.stride(0), y.data_ptr(), y.stride(0),
+                        0 if divisor is None else divisor.data_ptr(), dstride, 0 if weight is None else weight.data_ptr(), per_head,
+                        0 if eps is None else 1, 0.0 if eps is None else eps, gate_kind, rows, heads, size)
+    _check(_lib.gb_head_norm_gate(byref(p), _code(x.dtype), _code(y.dtype), _stream()))
 
 
 # ---- a whole pre-norm layer from one call ---------------------------------------------------

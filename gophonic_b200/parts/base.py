@@ -39,11 +39,13 @@ class TensorDecl:
 
 @dataclass(frozen=True)
 class KVRequest:
-    """Per token, per sequence: keys and values of ``kv_heads`` x ``head_dim``.
-    window = 0: every key is kept; w > 0: only the last w keys are ever read."""
+    """Per token, per sequence: keys of ``kv_heads`` x ``head_dim`` and values of ``kv_heads`` x
+    ``value_dim`` (``head_dim`` if 0).  window = 0: every key is kept; w > 0: only the last w keys
+    are ever read."""
     kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0
 
 
 @dataclass(frozen=True)

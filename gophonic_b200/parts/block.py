@@ -32,10 +32,11 @@ class PreNormBlock(Part):
         decls: List[TensorDecl] = []
         decls += registry.part_class("norm", layer.mixer_norm.kind).declare(layer.mixer_norm, p + layer.mixer_norm_prefix)
         decls += registry.part_class("mixer", layer.mixer.kind).declare(layer.mixer, p + layer.mixer_prefix)
-        decls += registry.part_class("norm", layer.feed_forward_norm.kind).declare(
-            layer.feed_forward_norm, p + layer.feed_forward_norm_prefix)
-        decls += registry.part_class("feed_forward", layer.feed_forward.kind).declare(
-            layer.feed_forward, p + layer.feed_forward_prefix)
+        if layer.feed_forward is not None:
+            decls += registry.part_class("norm", layer.feed_forward_norm.kind).declare(
+                layer.feed_forward_norm, p + layer.feed_forward_norm_prefix)
+            decls += registry.part_class("feed_forward", layer.feed_forward.kind).declare(
+                layer.feed_forward, p + layer.feed_forward_prefix)
         return decls
 
     def __init__(self, layer, prefix: str, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
@@ -46,10 +47,13 @@ class PreNormBlock(Part):
             layer.mixer_norm, p + layer.mixer_norm_prefix, tensors, runtime)
         self.mixer = registry.part_class("mixer", layer.mixer.kind)(
             layer.mixer, p + layer.mixer_prefix, tensors, runtime)
-        self.feed_forward_norm = registry.part_class("norm", layer.feed_forward_norm.kind)(
-            layer.feed_forward_norm, p + layer.feed_forward_norm_prefix, tensors, runtime)
-        self.feed_forward = registry.part_class("feed_forward", layer.feed_forward.kind)(
-            layer.feed_forward, p + layer.feed_forward_prefix, tensors, runtime)
+        # a layer without a feed-forward is its mixer sublayer alone
+        self.feed_forward_norm = self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = registry.part_class("norm", layer.feed_forward_norm.kind)(
+                layer.feed_forward_norm, p + layer.feed_forward_norm_prefix, tensors, runtime)
+            self.feed_forward = registry.part_class("feed_forward", layer.feed_forward.kind)(
+                layer.feed_forward, p + layer.feed_forward_prefix, tensors, runtime)
         self._native = None       # the library's record of this layer, if it can issue the layer itself
         self._native_tables = None
 
@@ -95,11 +99,11 @@ class PreNormBlock(Part):
         return [self.mixer]
 
     def weight_bytes(self) -> int:
-        return sum(p.weight_bytes() for p in (self.mixer, self.feed_forward) if hasattr(p, "weight_bytes"))
+        return sum(p.weight_bytes() for p in (self.mixer, self.feed_forward) if p is not None and hasattr(p, "weight_bytes"))
 
     @property
     def capturable(self) -> bool:
-        return all(p.capturable for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward))
+        return all(p.capturable for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None)
 
     def first_norm(self):
         """The norm that reads the residual first: whoever changes the residual ahead of this block
@@ -132,7 +136,8 @@ class PreNormBlock(Part):
             return ops.prenorm_layer_forward(native, batch, cache, h, pending if isinstance(pending, torch.Tensor) else None,
                                              work, splits, scratch)
         if folds:
-            pending = self.mixer.forward_folded(batch, h, pending, self.mixer_norm, cache, self.feed_forward_norm)
+            pending = self.mixer.forward_folded(batch, h, pending, self.mixer_norm, cache,
+                                                self.feed_forward_norm if self.feed_forward is not None else next_norm)
         else:
             x = torch.empty((rows, hidden), dtype=act, device=h.device)
             self.mixer_norm.forward(h, x, pending if isinstance(pending, torch.Tensor) else None)
@@ -142,6 +147,8 @@ class PreNormBlock(Part):
             else:
                 pending = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
                 self.mixer.forward(batch, x, pending, cache)
+        if self.feed_forward is None:
+            return pending
         if (isinstance(pending, RowStats) and pending.prescaled_for is self.feed_forward_norm
                 and self.feed_forward.folds_norm(rows, self.feed_forward_norm)):
             return self.feed_forward.forward_folded(batch, h, pending, self.feed_forward_norm, next_norm)

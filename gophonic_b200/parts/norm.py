@@ -15,12 +15,12 @@ class RMSNorm(Norm):
 
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
-        return [TensorDecl(prefix + "weight", (spec.size,), role="norm")]
+        return [TensorDecl(prefix + getattr(spec, "tensor", "weight"), (spec.size,), role="norm")]
 
     def __init__(self, spec, prefix: str, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         self.spec = spec
         self.rt = runtime
-        self.weight = tensors[prefix + "weight"].to(torch.float32).contiguous()
+        self.weight = tensors[prefix + getattr(spec, "tensor", "weight")].to(torch.float32).contiguous()
         self.eps = float(spec.eps)
 
     def rms_fold(self):

@@ -50,3 +50,22 @@ class NoPosition(PositionEncoding):
 
     def kernel_args(self):
         return None, None, 0
+
+
+class PairRotaryEmbedding(RotaryEmbedding):
+    """Rotary embedding in which channels 2i and 2i + 1 turn together by pos * theta^(-2i/rotary_dim)
+    (``RotaryEmbedding`` pairs i with i + rotary_dim / 2).  The angle tables are the same; the kernel
+    is told which channels belong together (``pairs``).  A rotary width of 0 rotates nothing."""
+    pairs = True
+
+    def __init__(self, spec, prefix, tensors, runtime: Runtime):
+        if spec.rotary_dim < 0 or spec.rotary_dim % 2 or spec.rotary_dim > spec.head_dim:
+            raise ValueError(f"rotary width {spec.rotary_dim} must be even and in [0, head_dim={spec.head_dim}]")
+        self.spec = spec
+        self.rt = runtime
+        self.cos = self.sin = None
+        self.capacity = 0
+
+    def prepare(self, capacity: int) -> None:
+        if self.spec.rotary_dim > 0:
+            super().prepare(capacity)

@@ -15,14 +15,21 @@ class SwiGLU(FeedForward):
 
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
-        return [TensorDecl(prefix + "gate_proj.weight", (spec.intermediate, spec.hidden)),
-                TensorDecl(prefix + "up_proj.weight", (spec.intermediate, spec.hidden)),
-                TensorDecl(prefix + "down_proj.weight", (spec.hidden, spec.intermediate))]
+        gate, up, down = cls.names(spec)
+        return [TensorDecl(prefix + gate, (spec.intermediate, spec.hidden)),
+                TensorDecl(prefix + up, (spec.intermediate, spec.hidden)),
+                TensorDecl(prefix + down, (spec.hidden, spec.intermediate))]
+
+    @staticmethod
+    def names(spec):
+        """Tensor names of the gate, up and down projections under the part's prefix."""
+        return getattr(spec, "names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
 
     def __init__(self, spec, prefix: str, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         self.spec = spec
         self.rt = runtime
-        gate, up = tensors[prefix + "gate_proj.weight"], tensors[prefix + "up_proj.weight"]
+        gate_name, up_name, down_name = self.names(spec)
+        gate, up = tensors[prefix + gate_name], tensors[prefix + up_name]
         if gate.dtype != up.dtype:
             raise ValueError(f"{prefix}: gate_proj is {gate.dtype} and up_proj is {up.dtype}; they must agree")
         # bfloat16 weights whose width allows it are kept with gate and up rows alternating in blocks
@@ -35,7 +42,7 @@ class SwiGLU(FeedForward):
                 .reshape(2 * inter, hidden).contiguous()
         else:
             self.gate_up = torch.cat([gate, up], dim=0).contiguous()
-        self.down = tensors[prefix + "down_proj.weight"].contiguous()
+        self.down = tensors[prefix + down_name].contiguous()
 
     def weight_bytes(self) -> int:
         return self.gate_up.numel() * self.gate_up.element_size() + self.down.numel() * self.down.element_size()

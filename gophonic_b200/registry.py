@@ -85,10 +85,13 @@ def architecture_of(config: Dict[str, Any]) -> str:
     archs = config.get("architectures")
     if isinstance(archs, list) and archs and archs[0] in _architectures:
         return archs[0]
+    one = config.get("architecture")      # some designs name themselves with one string
+    if isinstance(one, str) and one in _architectures:
+        return one
     mt = config.get("model_type")
     if mt in _model_types:
         return _model_types[mt]
-    named = archs[0] if isinstance(archs, list) and archs else mt
+    named = archs[0] if isinstance(archs, list) and archs else (one if isinstance(one, str) else mt)
     raise RegistryError(f"no architecture registered for '{named}'; registered: {architectures()}")
 
 
@@ -114,7 +117,9 @@ def read_config(model_dir: str):
 
 def _register_builtin() -> None:
     from .config.qwen3 import Qwen3Config
+    from .config.pugalix import PugalixConfig
     register_architecture("Qwen3ForCausalLM", Qwen3Config, model_type="qwen3")
+    register_architecture("Pugalix", PugalixConfig)
 
 
 _register_builtin()

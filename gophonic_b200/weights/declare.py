@@ -7,6 +7,15 @@ from .. import registry
 from ..parts.base import TensorDecl
 
 
+def final_norm_prefix(spec) -> str:
+    """The prefix under which the final norm resolves its tensor: the tensor's full name less the
+    suffix the norm's spec names (``weight`` unless the spec says otherwise)."""
+    name, suffix = spec.final_norm_name, getattr(spec.final_norm, "tensor", "weight")
+    if not name.endswith(suffix):
+        raise ValueError(f"final norm tensor name '{name}' must end in '{suffix}'")
+    return name[:len(name) - len(suffix)]
+
+
 def declare_model(spec) -> List[TensorDecl]:
     """Every tensor of ``spec`` by checkpoint name: embedding, each layer's parts (each layer once,
     however often the schedule runs it), final norm, and the head (optional when it can be tied)."""
@@ -15,10 +24,7 @@ def declare_model(spec) -> List[TensorDecl]:
                                           role="embedding")]
     for layer in spec.layers:
         decls += registry.part_class("block", layer.block).declare(layer)
-    norm_name = spec.final_norm_name
-    if not norm_name.endswith("weight"):
-        raise ValueError(f"final norm tensor name '{norm_name}' must end in 'weight'")
-    decls += registry.part_class("norm", spec.final_norm.kind).declare(spec.final_norm, norm_name[:-len("weight")])
+    decls += registry.part_class("norm", spec.final_norm.kind).declare(spec.final_norm, final_norm_prefix(spec))
     decls.append(TensorDecl(spec.head.name, (spec.head.vocab, spec.head.hidden), role="matrix",
                             optional=spec.head.tied_to is not None))
     seen = set()

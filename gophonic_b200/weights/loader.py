@@ -66,7 +66,8 @@ def check(ckpt: Checkpoint, decls: Sequence[TensorDecl], strict: bool = False) -
         e = ckpt.tensors.get(d.name)
         if e is None:
             continue
-        if tuple(e.shape) != tuple(d.shape):
+        # a size the declaration leaves open (None) is whatever the checkpoint has
+        if len(e.shape) != len(d.shape) or any(want is not None and got != want for got, want in zip(e.shape, d.shape)):
             wrong_shape.append(f"{d.name} has shape {list(e.shape)}, want {list(d.shape)}")
         ok = _INT if d.role == "table" else _FLOAT
         if e.dtype not in ok:

@@ -100,9 +100,15 @@ def counter_fill(key: int, n: int, std: float, mean: float) -> np.ndarray:
     return out
 
 
+def _sized(d: TensorDecl) -> None:
+    if any(n is None for n in d.shape):
+        raise ValueError(f"random weights: the configuration leaves a size of '{d.name}' {d.shape} to the checkpoint; name it")
+
+
 def random_tensor(d: TensorDecl, seed: int, scales: InitScales, head_name: Optional[str] = None) -> np.ndarray:
     """fp32 values of one declared tensor."""
     std, mean = _std_and_mean(d, scales, head_name)
+    _sized(d)
     return counter_fill(_tensor_seed(seed, d.name), int(np.prod(d.shape)), std, mean).reshape(d.shape)
 
 
@@ -157,6 +163,7 @@ def random_tensors_on_device(spec, seed: int, mode: str, device, scales: InitSca
         if d.role == "table":
             raise ValueError(f"random weights: no rule for the integer table {d.name}")
         std, mean = _std_and_mean(d, scales, spec.head.name)
+        _sized(d)
         t = torch.empty(d.shape, dtype=torch.bfloat16, device=device)   # what a BF16 checkpoint stores
         ops.random_fill(t, _tensor_seed(seed, d.name), float(fill_constant(std)), float(mean))
         out[d.name] = place(t, "BF16", d.role, mode, device)

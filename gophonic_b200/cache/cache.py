@@ -7,8 +7,8 @@ Within a page the layout is [kv_head][64][head_dim], so one head's 64 keys are o
 block.  A block table [slot][logical page] -> physical page, mirrored on the device, is shared
 by every group: page p of a sequence is physical page table[slot][p] in every plane.
 
-Groups.  Runs of layers are grouped by what they need: (kv_heads, head_dim, window, value_dim) for
-key/value planes (a value head may have another size than a key head), (shape, dtype) for fixed-size state.  Each group has storage of its own; a run
+Groups.  Runs of layers are grouped by what they need: (kv_heads, head_dim, window) for
+key/value planes (and the size of a value head where it is not a key head's), (shape, dtype) for fixed-size state.  Each group has storage of its own; a run
 is given the plane with its ordinal inside its group (the reference indexes KV planes the same
 way, by a layer's place among layers of its kind: internal/qwen3lm/gpu_darwin.go:51-55, 270-277,
 831, and keeps per-sequence state beside K/V: gpu_darwin.go:800-808).  A run that reads another
@@ -156,7 +156,10 @@ class Cache:
             if cache_of is not None or req is None:
                 continue
             if isinstance(req, KVRequest):
-                key = (req.kv_heads, req.head_dim, req.window, req.value_dim or req.head_dim)
+                # values as wide as keys: the key every such group has always had; else the width is part of it
+                key = (req.kv_heads, req.head_dim, req.window)
+                if req.value_dim and req.value_dim != req.head_dim:
+                    key += (req.value_dim,)
                 planes = self._kv_groups.setdefault(key, [])
                 self._plane[pos] = ("kv", key, len(planes))
                 planes.append(pos)
@@ -173,7 +176,7 @@ class Cache:
         self._k: Dict[Tuple[int, ...], torch.Tensor] = {}
         self._v: Dict[Tuple[int, ...], torch.Tensor] = {}
         for key, planes in self._kv_groups.items():
-            kvh, d, _w, dv = key
+            kvh, d, dv = key[0], key[1], key[-1] if len(key) == 4 else key[1]
             self._k[key] = torch.zeros((len(planes), self.n_pages + 1, kvh, PAGE, d), dtype=dtype, device=self.device)
             self._v[key] = torch.zeros((len(planes), self.n_pages + 1, kvh, PAGE, dv), dtype=dtype, device=self.device)
         self._state: Dict[Tuple[Tuple[int, ...], torch.dtype], torch.Tensor] = {}
@@ -191,7 +194,8 @@ class Cache:
     # ---- description -------------------------------------------------------------------
     def groups(self) -> List[dict]:
         out = []
-        for (kvh, d, w, dv), planes in self._kv_groups.items():
+        for key, planes in self._kv_groups.items():
+            kvh, d, w, dv = key[0], key[1], key[2], key[-1] if len(key) == 4 else key[1]
             out.append({"kind": "kv", "kv_heads": kvh, "head_dim": d, "value_dim": dv, "window": w, "planes": list(planes),
                         "bytes_per_token": len(planes) * kvh * (d + dv) * torch.empty((), dtype=self.dtype).element_size()})
         for (shape, sdtype), planes in self._state_groups.items():

@@ -98,6 +98,24 @@ def visible(i: int, j: int, size: int, keep_first: int) -> bool:
     return j <= i and (i - j < size or j < keep_first)
 
 
+def windowed_sink_attention(q, k, v, scale, size, keep_first, first_pos: int = 0):
+    """q [Tq, H, d] at positions first_pos.., k [Tk, G, d], v [Tk, G, dv] at positions 0..: per head
+    softmax((q . k) scale) over the visible keys with one more unit in the denominator; [Tq, H, dv]."""
+    Tq, H, _ = q.shape
+    Tk, G, dv = v.shape
+    mask = np.array([[visible(first_pos + i, j, size, keep_first) for j in range(Tk)] for i in range(Tq)])
+    out = np.zeros((Tq, H, dv))
+    for head in range(H):
+        g = head // (H // G)
+        s = (q[:, head, :] @ k[:, g, :].T) * scale
+        s = np.where(mask, s, -np.inf)
+        top = np.maximum(s.max(axis=1, keepdims=True), 0.0)
+        e = np.exp(s - top)
+        denom = np.exp(-top) + e.sum(axis=1, keepdims=True)      # the sink: one more unit, no value
+        out[:, head, :] = (e / denom) @ v[:, g, :]
+    return out
+
+
 def attention_keys_values(h, w, p, m):
     """Rotated keys [T, G, d] and values [T, G, dv] of an attention layer with projections of its own."""
     T = h.shape[0]
@@ -116,17 +134,7 @@ def attention_mixer(h, w, p, m, kv):
     q = (h @ w[p + "q"].T + w[p + "q.b"]).reshape(T, H, d)
     q = rotate_pairs(q, np.arange(T), m["rot"]["dims"], m["rot"]["base"])
     k, v = kv
-    size, keep = m["mask"]["size"], m["mask"]["keep_first"]
-    mask = np.array([[visible(i, j, size, keep) for j in range(T)] for i in range(T)])
-    out = np.zeros((T, H, dv))
-    for head in range(H):
-        g = head // (H // G)
-        s = (q[:, head, :] @ k[:, g, :].T) * m["scale"]
-        s = np.where(mask, s, -np.inf)
-        top = np.maximum(s.max(axis=1, keepdims=True), 0.0)
-        e = np.exp(s - top)
-        denom = np.exp(-top) + e.sum(axis=1, keepdims=True)      # the sink: one more unit, no value
-        out[:, head, :] = (e / denom) @ v[:, g, :]
+    out = windowed_sink_attention(q, k, v, m["scale"], m["mask"]["size"], m["mask"]["keep_first"])
     gate = sigmoid(h @ w[p + "g"].T)
     return (out.reshape(T, H * dv) * gate) @ w[p + "o"].T
 
@@ -215,3 +223,96 @@ def forward(cfg: dict, w: Dict[str, np.ndarray], tokens, return_layers: bool = F
         after.append(x.copy())
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, np.stack(after)) if return_layers else logits
+
+
+# ---- making test models (own writer, so the tests share nothing with the library's) ----------
+def tensor_shapes(cfg: dict, rank: int = 8) -> Dict[str, tuple]:
+    """Every tensor of a Pugalix checkpoint by name; ``rank``: rows of a gla mixer's first decay matrix
+    where the configuration does not say."""
+    W, V = cfg["width"], cfg["vocab"]
+    out = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
+    for i, layer in enumerate(cfg["layers"]):
+        m, p = layer["mixer"], f"l{i}.mix."
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        out[f"l{i}.norm1"] = (W,)
+        out.update({p + "q": (H * d, W), p + "g": (H * dv, W), p + "o": (W, H * dv)})
+        if layer["type"] == "attention":
+            G = m["kv_heads"]
+            out[p + "q.b"] = (H * d,)
+            if m.get("kv_from") is None:
+                out.update({p + "k": (G * d, W), p + "k.b": (G * d,), p + "v": (G * dv, W), p + "v.b": (G * dv,)})
+        else:
+            out.update({p + "k": (H * d, W), p + "v": (H * dv, W)})
+            if layer["type"] == "gla":
+                r = m.get("rank", rank)
+                out.update({p + "norm": (dv,), p + "a1": (r, W), p + "a2": (H * d, r), p + "a2.b": (H * d,)})
+            else:
+                out.update({p + "norm": (H * dv,), p + "i": (H, W), p + "i.b": (H,), p + "f": (H, W), p + "f.b": (H,)})
+        if layer.get("mlp") is not None:
+            F = layer["mlp"]["ff"]
+            out[f"l{i}.norm2"] = (W,)
+            out.update({f"l{i}.mlp.gate": (F, W), f"l{i}.mlp.up": (F, W), f"l{i}.mlp.down": (W, F)})
+    return out
+
+
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """float -> bfloat16 bit patterns, round to nearest even."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16_bits(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+
+def random_weights(cfg: dict, seed: int, rank: int = 8) -> Dict[str, np.ndarray]:
+    """Random weights whose values bfloat16 holds exactly: matrices of deviation 1/sqrt(inputs), norm
+    weights near 1, biases that matter, decays and forget gates that keep a state alive for a while."""
+    rng = np.random.default_rng(seed)
+    w = {}
+    for name, shape in tensor_shapes(cfg, rank).items():
+        last = name.rsplit(".", 1)[-1]
+        if last in ("norm", "norm1", "norm2"):
+            v = 1.0 + 0.2 * rng.standard_normal(shape)
+        elif name.endswith("a2.b"):
+            v = 2.0 + rng.standard_normal(shape)
+        elif name.endswith("f.b"):
+            v = 2.0 + rng.standard_normal(shape)
+        elif name.endswith(".b"):
+            v = 0.5 * rng.standard_normal(shape)
+        elif name == "embed":
+            v = rng.standard_normal(shape)
+        else:
+            v = rng.standard_normal(shape) / math.sqrt(shape[-1])
+        w[name] = from_bf16_bits(to_bf16_bits(v)).reshape(shape)
+    return w
+
+
+def write_model(model_dir: str, cfg: dict, w: Dict[str, np.ndarray]) -> str:
+    """config.json and model.safetensors (bfloat16) of a model whose weights bfloat16 holds exactly."""
+    os.makedirs(model_dir, exist_ok=True)
+    header, blobs, at = {}, [], 0
+    for name in sorted(w):
+        raw = to_bf16_bits(w[name]).astype("<u2").tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(w[name].shape), "data_offsets": [at, at + len(raw)]}
+        blobs.append(raw)
+        at += len(raw)
+    text = json.dumps(header, separators=(",", ":")).encode()
+    text += b" " * (-len(text) % 8)
+    with open(os.path.join(model_dir, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(text)) + text + b"".join(blobs))
+    with open(os.path.join(model_dir, "config.json"), "w") as f:
+        json.dump(cfg, f, indent=1)
+    return model_dir
+
+
+def greedy_generate(cfg, w, prompt, n: int) -> Tuple[List[int], List[float]]:
+    """``n`` greedy tokens after ``prompt`` and, for each, the margin of its logit over the runner-up."""
+    ids, out, margins = list(prompt), [], []
+    for _ in range(n):
+        logits = forward(cfg, w, ids)[-1]
+        order = np.argsort(logits)
+        out.append(int(order[-1]))
+        margins.append(float(logits[order[-1]] - logits[order[-2]]))
+        ids.append(out[-1])
+    return out, margins

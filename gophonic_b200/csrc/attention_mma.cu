@@ -78,6 +78,11 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
         if (lo_pos < 0) lo_pos = 0;
     }
     const int t_lo = lo_pos / 64, t_hi = hi_pos / 64;
+    // with kept first tokens: the tiles of keys [0, keep_first) first, then those of the window, each once
+    int n_first = p.window > 0 && p.keep_first > 0 ? (p.keep_first + 63) / 64 : 0;
+    if (n_first > t_lo) n_first = t_lo;
+    const int n_tiles = n_first + t_hi - t_lo + 1;
+    auto tile_of = [&](int i) { return i < n_first ? i : t_lo + (i - n_first); };
 
     auto load_tile = [&](int t, int buf) {
         int64_t page = page_of(bt, t * 64, p.bt_stride, p.pages);
@@ -85,7 +90,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
         load_page<HD>(Ks + buf * 64 * SD, kbase + off, tid, 128);
         load_page<HD>(Vs + buf * 64 * SD, vbase + off, tid, 128);
     };
-    load_tile(t_lo, 0);
+    load_tile(tile_of(0), 0);
     cp_async_commit();
 
     const float sc = p.scale * LOG2E;
@@ -99,13 +104,14 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
         for (int e = 0; e < 4; e++) o[j][e] = 0.f;
     uint32_t qf[QREG ? KS : 1][4];
 
-    for (int t = t_lo; t <= t_hi; t++) {
-        const int buf = (t - t_lo) & 1;
+    for (int ti = 0; ti < n_tiles; ti++) {
+        const int t = tile_of(ti);
+        const int buf = ti & 1;
         cp_async_wait<0>();
         __syncthreads();
-        if (t + 1 <= t_hi) load_tile(t + 1, buf ^ 1);
+        if (ti + 1 < n_tiles) load_tile(tile_of(ti + 1), buf ^ 1);
         cp_async_commit();
-        if (QREG && t == t_lo) {
+        if (QREG && ti == 0) {
 #pragma unroll
             for (int ks = 0; ks < KS; ks++)
                 ldmatrix_x4(qf[QREG ? ks : 0], Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks * 16 + (lane >> 4) * 8);
@@ -142,7 +148,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
             for (int e = 0; e < 4; e++) {
                 int key = t * 64 + j * 8 + t4 * 2 + (e & 1);
                 int row = (e & 2) ? row1 : row0;
-                bool ok = key <= row && (p.window <= 0 || key > row - p.window);
+                bool ok = key <= row && (p.window <= 0 || key > row - p.window || key < p.keep_first);
                 float v = ok ? s[j][e] * sc : -INFINITY;
                 s[j][e] = v;
                 if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
@@ -191,6 +197,20 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (p.sink) {
+        // one more unit in the denominator: a key of score 0 that has no value
+        const float f0 = fmaxf(m0, 0.f), f1 = fmaxf(m1, 0.f);
+        const float k0 = exp2f(m0 - f0), k1 = exp2f(m1 - f1);
+        l0 = l0 * k0 + exp2f(-f0);
+        l1 = l1 * k1 + exp2f(-f1);
+#pragma unroll
+        for (int j = 0; j < NF; j++) {
+            o[j][0] *= k0;
+            o[j][1] *= k0;
+            o[j][2] *= k1;
+            o[j][3] *= k1;
+        }
+    }
     const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;
     bf16* ob = (bf16*)p.out + (int64_t)head * HD;
     if (r0 < q_len) {
@@ -320,13 +340,19 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
         if (lo_pos < 0) lo_pos = 0;
     }
     const int t_lo = lo_pos / 64, t_hi = pos / 64 + 1;  // [t_lo, t_hi)
-    const int per = (t_hi - t_lo + p.num_splits - 1) / p.num_splits;
-    const int my_lo = t_lo + split * per;
-    const int my_hi = my_lo + per < t_hi ? my_lo + per : t_hi;
+    // with kept first tokens: the tiles of keys [0, keep_first) first, then those of the window; the
+    // splits cut this list of tiles
+    int n_first = p.window > 0 && p.keep_first > 0 ? (p.keep_first + 63) / 64 : 0;
+    if (n_first > t_lo) n_first = t_lo;
+    const int n_tiles = n_first + t_hi - t_lo;
+    auto tile_of = [&](int i) { return i < n_first ? i : t_lo + (i - n_first); };
+    const int per = (n_tiles + p.num_splits - 1) / p.num_splits;
+    const int my_lo = split * per;
+    const int my_hi = my_lo + per < n_tiles ? my_lo + per : n_tiles;
     const int n = my_hi > my_lo ? my_hi - my_lo : 0;
 
     auto load_tile = [&](int i) {
-        int t = my_lo + i;
+        int t = tile_of(my_lo + i);
         int64_t page = page_of(bt, t * 64, p.bt_stride, p.pages);
         int64_t off = ((page * p.kv_heads + kvh) * 64) * (int64_t)HD;
         bf16* st = KV + (i % DSTAGES) * STAGE;
@@ -356,7 +382,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
     // The CTA whose keys end with the token's own page has that key and value from the q/k/v product's
     // row, not from the cache: the last tile is patched in shared memory, and one CTA per kv head also
     // stores them in the cache for the steps to come.
-    const bool owns_last = f.on && f.write_kv && n > 0 && my_hi == t_hi;  // a run that only reads another's cache finds the key there
+    const bool owns_last = f.on && f.write_kv && n > 0 && my_hi == n_tiles;  // a run that only reads another's cache finds the key there
     if (f.on && n > 0) {
         const int half = f.rot / 2;
         // rows whose position lies beyond the table are refused on the host
@@ -428,7 +454,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
         }
         const bf16* kt = KV + (i % DSTAGES) * STAGE;
         const bf16* vt = kt + 64 * SD;
-        const int t = my_lo + i;
+        const int t = tile_of(my_lo + i);
         float s[2][4];
 #pragma unroll
         for (int j = 0; j < 2; j++)
@@ -453,7 +479,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
 #pragma unroll
             for (int e = 0; e < 4; e++) {
                 int key = t * 64 + warp * 16 + j * 8 + t4 * 2 + (e & 1);
-                bool ok = key <= pos && key >= lo_pos;
+                bool ok = key <= pos && (key >= lo_pos || key < p.keep_first);
                 float v = ok ? s[j][e] * sc : -INFINITY;
                 s[j][e] = v;
                 if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
@@ -526,6 +552,11 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
         int r = idx / HD, c = idx - r * HD;
         float M = fmaxf(fmaxf(Ms[r], Ms[16 + r]), fmaxf(Ms[32 + r], Ms[48 + r]));
         float L = 0.f, acc = 0.f;
+        const bool sink_here = p.sink && p.num_splits == 1;   // with key splits the merge kernel adds the sink's unit
+        if (sink_here) {
+            M = fmaxf(M, 0.f);
+            L = exp2f(-M);
+        }
         if (M != -INFINITY) {
 #pragma unroll
             for (int w = 0; w < 4; w++) {
@@ -595,7 +626,7 @@ int launch_decode(const AttnParams& p, const RopeFuse& f, cudaStream_t stream) {
     GB_CHECK_LAUNCH("attention_decode_mma");
     if (p.num_splits > 1)
         return gb_attention_merge_launch(p.scratch, p.out, GB_BF16, p.out_row_stride, p.seq_q_start, p.nseq, p.heads, p.d,
-                                         p.num_splits, 0, stream);
+                                         p.num_splits, p.sink, stream);
     return 0;
 }
 
@@ -604,8 +635,8 @@ int check(const AttnParams& p, const char* who) {
     if (p.d % 16 || p.d < 16 || (p.d > 128 && p.d != 256))
         GB_REFUSE("%s: head_dim %d is not one of 16, 32, ..., 128, 256 (other sizes up to 256 run on the CUDA-core kernel)", who, p.d);
     if (p.window < 0) GB_REFUSE("%s: window %d", who, p.window);
-    if ((p.dv && p.dv != p.d) || p.keep_first || p.sink)
-        GB_REFUSE("%s: values of another size than keys, kept first tokens and a sink run on the CUDA-core kernel", who);
+    if (p.dv && p.dv != p.d) GB_REFUSE("%s: values of another size than keys run on the CUDA-core kernel", who);
+    if (p.keep_first < 0) GB_REFUSE("%s: %d kept first tokens", who, p.keep_first);
     if (((uintptr_t)p.q & 15) || (p.q_row_stride & 7)) GB_REFUSE("%s: query rows must be 16-byte aligned", who);
     if ((p.out_row_stride & 1) || ((uintptr_t)p.out & 3)) GB_REFUSE("%s: output rows must be 4-byte aligned", who);
     return 0;

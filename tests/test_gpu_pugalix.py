@@ -47,6 +47,11 @@ CONFIGS = {
     # the four kinds of layer together; the last attention layer reads the first one's keys with a
     # window and kept tokens of its own
     "mix": config([gla(ff=96), attention(), mlstm(), attention(size=9, keep=0, kv_from=1, ff=80), gla(heads=4, dim=8, vdim=8, tau=2.0)]),
+    # key and value heads of one size that the tensor-core attention kernels take in bfloat16 (32, 64),
+    # grouped heads, a window shorter and longer than a page
+    "tensor": config([attention(heads=4, kv_heads=2, dim=32, vdim=32, rot=8, size=40, keep=2, ff=64), mlstm(heads=2, dim=16, vdim=16),
+                      attention(heads=6, kv_heads=2, dim=64, vdim=64, rot=64, size=100, keep=70, scale=0.1),
+                      attention(heads=6, kv_heads=2, dim=64, vdim=64, rot=64, size=7, keep=1, scale=0.1, kv_from=2)], width=96, vocab=80),
     # sizes that are odd, equal, or 1: one head everywhere, key and value sizes equal in attention and not
     # multiples of 8 elsewhere, the whole head rotated, more kept tokens than the window is long
     "odd": config([attention(heads=1, kv_heads=1, dim=24, vdim=24, rot=24, size=5, keep=8, scale=0.31, ff=56),
@@ -107,10 +112,10 @@ TOL = {"float32": 3e-5, "bfloat16": 6e-2}
 
 # ---- each mechanism alone, and all together ---------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["attention", "gla", "mlstm", "mix", "odd"])
+@pytest.mark.parametrize("name", ["attention", "gla", "mlstm", "mix", "odd", "tensor"])
 def test_whole_prompts_match_the_plain_model(models, name, dtype):
     cfg, w, _ = models[name]
-    toks = tokens_for(cfg, 1, 150)
+    toks = tokens_for(cfg, 1, 230 if name == "tensor" else 150)
     close(feed(engine_for(models, name, dtype), toks), P.forward(cfg, w, toks), TOL[dtype])
 
 
@@ -151,10 +156,11 @@ def test_token_by_token_equals_the_whole_prompt(models, name, graphs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mix", "tensor"])
 @pytest.mark.parametrize("cuts", [[2] * 40, [3, 64, 1, 2, 61], [63, 1, 1, 64], [130, 2]])
-def test_portions_of_a_prompt(models, cuts, dtype):
-    cfg, w, _ = models["mix"]
-    eng = engine_for(models, "mix", dtype)
+def test_portions_of_a_prompt(models, cuts, dtype, name):
+    cfg, w, _ = models[name]
+    eng = engine_for(models, name, dtype)
     toks = tokens_for(cfg, 4, 140)
     got = feed(eng, toks, cuts=cuts)
     close(got, P.forward(cfg, w, toks), TOL[dtype])
@@ -209,12 +215,13 @@ def test_slots_and_pages_that_are_used_again(models):
     close(got, P.forward(cfg, w, b[:20]), TOL["float32"])
 
 
-def test_long_decoding_past_windows_and_pages(models):
-    cfg, w, _ = models["mix"]
+@pytest.mark.parametrize("name", ["mix", "tensor"])
+def test_long_decoding_past_windows_and_pages(models, name):
+    cfg, w, _ = models[name]
     toks = tokens_for(cfg, 5, 40 + 230)
     want = P.forward(cfg, w, toks)
     for dtype in ("float32", "bfloat16"):
-        got = feed(engine_for(models, "mix", dtype), toks, cuts=[40] + [1] * 230)
+        got = feed(engine_for(models, name, dtype), toks, cuts=[40] + [1] * 230)
         close(got, want, TOL[dtype])
 
 
@@ -262,7 +269,8 @@ def _attention_case(rng, T, heads, kv_heads, d, dv, window, keep):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("shape", [(2, 1, 16, 8, 37, 5), (4, 4, 24, 24, 70, 0), (3, 1, 8, 40, 64, 64)])
+@pytest.mark.parametrize("shape", [(2, 1, 16, 8, 37, 5), (4, 4, 24, 24, 70, 0), (3, 1, 8, 40, 64, 64),
+                                   (4, 2, 32, 32, 70, 5), (2, 1, 64, 64, 37, 66), (3, 3, 128, 128, 130, 1)])
 def test_attention_kernel_at_the_edges(shape, dtype):
     import torch
     from gophonic_b200 import ops

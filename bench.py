@@ -279,6 +279,127 @@ def further_model_points(name, steps, torch, ops, hbm_peak, tflops_peak):
     return out
 
 
+# ---- another design beside its closest model ---------------------------------------------------
+DESIGN_TWINS = {"pugalix-2k": "1.7b", "pugalix-4k": "8b"}      # the same width, heads, head size, feed-forward and vocabulary
+OP_CLASSES = ("gemm", "gemm_add", "gemm_swiglu", "gemm_scaled", "gemm_residual", "attention", "attention_decode_rope",
+              "qk_norm_rope_kv_write", "state_scan", "head_norm_gate", "gla_decay", "add_rmsnorm", "embed_gather", "swiglu",
+              "prenorm_layer_forward")
+
+
+class OpTimer:
+    """Device time of every call into the kernel library during one eager step, by entry point (CUDA
+    events around each call; the calls of a step run one after the other on one stream)."""
+
+    def __init__(self, ops, torch):
+        self.ops, self.torch, self.saved, self.events = ops, torch, {}, []
+
+    def __enter__(self):
+        for name in OP_CLASSES:
+            fn = getattr(self.ops, name)
+            self.saved[name] = fn
+
+            def timed(*a, _fn=fn, _name=name, **k):
+                e0, e1 = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = _fn(*a, **k)
+                e1.record()
+                self.events.append((_name, e0, e1))
+                return out
+            setattr(self.ops, name, timed)
+        return self
+
+    def __exit__(self, *exc):
+        for name, fn in self.saved.items():
+            setattr(self.ops, name, fn)
+
+    def totals(self):
+        self.torch.cuda.synchronize()
+        out = {}
+        for name, e0, e1 in self.events:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        return {k: round(v * 1e3, 1) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
+
+
+def design_model(name, layers, torch):
+    from gophonic_b200 import registry
+    from gophonic_b200.config.presets import preset
+    from gophonic_b200.engine import Model
+    raw = dict(preset(name))
+    if "max_position_embeddings" in raw:
+        raw["max_position_embeddings"] = max(int(raw["max_position_embeddings"]), 8192)
+    cfg = registry.config_class(registry.architecture_of(raw)).from_dict(raw).with_layers(layers)
+    return cfg, Model.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0")
+
+
+def design_points(name, layers, steps, warmup, batches, context, torch, ops):
+    """Prompt and decode throughput of one named configuration with ``layers`` layers, and where the
+    device time of one prompt step and one decode step goes, by kernel-library entry point."""
+    from gophonic_b200.engine import Engine
+    from gophonic_b200.sampling import DeviceSampler
+    import numpy as np
+    cfg, model = design_model(name, layers, torch)
+    vocab = model.spec.vocab
+    out = {"layers": layers, "weights_gb": round(model.weight_bytes_per_step() / 1e9, 3)}
+    engine = Engine(model, max_tokens=max(batches) * context, max_slots=max(batches), max_seq_tokens=context)
+    fill_cache_random(engine, torch)
+    sampler = DeviceSampler(vocab, max(batches), engine.device)
+    for T in (512, PREFILL_TOKENS):
+        ms = time_prefill(engine, T, iters=3, warmup=3, torch=torch)
+        out[f"prefill_{T}_tok_s"] = round(T / (ms * 1e-3), 1)
+        out[f"prefill_{T}_ms"] = round(ms, 3)
+    for b in batches:
+        d = time_decode(engine, sampler, b, steps, warmup, torch, ops)
+        out[f"decode_b{b}_tok_s"] = round(b / (d["ms"] * 1e-3), 1)
+        out[f"decode_b{b}_ms"] = round(d["ms"], 4)
+    del engine
+    torch.cuda.empty_cache()
+    # the same steps issued kernel by kernel (no graph), each call into the library timed by itself
+    engine = Engine(model, max_tokens=8 * context, max_slots=8, max_seq_tokens=context, use_graphs=False)
+    fill_cache_random(engine, torch)
+    prompt = np.random.default_rng(1).integers(0, vocab, size=PREFILL_TOKENS).tolist()
+    slot = engine.new_sequence()
+    engine.step([(slot, prompt)])
+    engine.end_sequence(slot)
+    slot = engine.new_sequence()
+    with OpTimer(ops, torch) as t:
+        engine.step([(slot, prompt)])
+    out[f"prefill_{PREFILL_TOKENS}_us_by_op"] = t.totals()
+    engine.end_sequence(slot)
+    slots = decode_setup(engine, 8, context - 8, torch)
+    engine.step([(s, [1]) for s in slots])
+    with OpTimer(ops, torch) as t:
+        engine.step([(s, [1]) for s in slots])
+    out["decode_b8_us_by_op"] = t.totals()
+    for s in slots:
+        engine.end_sequence(s)
+    del engine, sampler, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def design_bench(args):
+    """``--design NAME``: the named configuration of another design beside the closest Qwen3-shaped one, the
+    same number of layers each; one JSON line."""
+    import torch
+    from gophonic_b200 import ops
+    if args.design not in DESIGN_TWINS:
+        print(json.dumps({"error": f"--design takes one of {sorted(DESIGN_TWINS)}"}))
+        return 2
+    layers = args.layers or 8
+    hbm_peak, tflops_peak, which = peaks()
+    batches = [int(b) for b in args.points.split(",") if b] + [args.batch]
+    clocks = ClockSampler()
+    clocks.start()
+    line = {"design": args.design, "twin": DESIGN_TWINS[args.design], "dtype": "bf16", "context": args.context,
+            "data": "synthetic: seeded random weights, random token ids, cache pre-filled with random keys/values",
+            "peaks": {"hbm_gbs": hbm_peak, "bf16_tflops": tflops_peak, "which": which}}
+    for key, name in (("design_points", args.design), ("twin_points", DESIGN_TWINS[args.design])):
+        line[key] = design_points(name, layers, args.steps, max(3, args.warmup), sorted(set(batches)), args.context, torch, ops)
+    line["clocks"] = clocks.stop()
+    print(json.dumps(line))
+    return 0
+
+
 def probe(name, **opts):
     """Run one kernel of the step a few times on a small, fixed workload (operands larger than L2
     where the kernel is bound by memory), for profilers.  Prints the kernel's own timing."""
@@ -460,7 +581,11 @@ def main():
     ap.add_argument("--profile", action="store_true", help="time each hot kernel alone and print its fraction of the roofline")
     ap.add_argument("--probe", default="", help="run one kernel on a small fixed workload (for profilers) and exit")
     ap.add_argument("--prompt-tokens", type=int, default=PREFILL_TOKENS, help="prompt length of --probe prefill_step")
+    ap.add_argument("--design", default="", help="instead of the headline run: a named configuration of another design "
+                    f"({', '.join(sorted(DESIGN_TWINS))}) beside the closest Qwen3-shaped one, --layers layers each (default 8)")
     args = ap.parse_args()
+    if args.design:
+        return design_bench(args)
     if args.probe:
         return probe(args.probe, model=args.model, batch=args.batch, context=args.context, prompt_tokens=args.prompt_tokens)
     if args.profile:

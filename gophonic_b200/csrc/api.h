@@ -92,6 +92,7 @@ struct LinearStateParams {
     int nseq, heads, d, dv;
     int scalar_decay;
     int max_slots;
+    int max_q_len;          // most rows a sequence brings; 1 selects the kernel for single tokens
 };
 
 // y = norm(x / divisor) * weight * gate(g) per (row, head); one warp a head.

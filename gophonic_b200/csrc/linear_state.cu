@@ -26,6 +26,8 @@ constexpr int COLS = 16;     // value columns per CTA
 constexpr int SLICES = 8;    // slices of the key channels
 constexpr int TT = 8;        // tokens staged at a time
 constexpr int THREADS = 128;
+static_assert(TT * COLS == THREADS, "a thread fetches one value of a tile");
+static_assert(TT == SLICES, "the exchange that adds the slices up leaves one token's sum with each slice");
 
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
@@ -113,8 +115,22 @@ __global__ void __launch_bounds__(THREADS) state_scan_kernel(LinearStateParams p
     float* S = p.state + (int64_t)slot * p.slot_stride + (int64_t)h * p.head_stride;
     float* nvec = S + (int64_t)d * dv;
 
-    // the state block of this CTA, through shared memory so that global rows are read whole
-    for (int idx = tid; idx < SLICES * RC * COLS; idx += THREADS) {
+    // the state block of this CTA, through shared memory so that global rows are read whole: 16 bytes a
+    // thread where the block's rows are whole and aligned
+    const bool vec = !norm_col && !(dv & 3) && j0 + COLS <= dv && !((uintptr_t)(S + j0) & 15);
+    if (vec) {
+#pragma unroll 4
+        for (int idx = tid; idx < SLICES * RC * (COLS / 4); idx += THREADS) {
+            const int c = idx / (COLS / 4), q4 = idx % (COLS / 4);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < d) v = *reinterpret_cast<const float4*>(S + (int64_t)c * dv + j0 + 4 * q4);
+            st_s[c][4 * q4] = v.x;
+            st_s[c][4 * q4 + 1] = v.y;
+            st_s[c][4 * q4 + 2] = v.z;
+            st_s[c][4 * q4 + 3] = v.w;
+        }
+    }
+    for (int idx = tid; !vec && idx < SLICES * RC * COLS; idx += THREADS) {
         const int c = idx / COLS, jj = idx % COLS;
         float v = 0.f;
         if (c < d) {
@@ -131,45 +147,78 @@ __global__ void __launch_bounds__(THREADS) state_scan_kernel(LinearStateParams p
     for (int i = 0; i < RC; i++) st[i] = st_s[slice * RC + i][col];
 
     const T* base = (const T*)p.qkv;
+    // A tile's rows are fetched into registers while the tile before it is worked on, and put into
+    // shared memory between two barriers: the global loads' latency hides behind the arithmetic.
+    constexpr int PER = TT * SLICES * RC / THREADS;   // q/k/decay elements a thread fetches per tile
+    // Every load of a fetch is unconditional (indices clamped into the tile) and nothing is done with the
+    // values until they are stored: they are all in flight at once.  What lies outside the tile or the
+    // head is replaced when it is stored: a token or channel that is not there changes nothing (decay 1, key 0).
+    T rq[PER], rk[PER], rv;
+    float ra[PER], rkeep = 1.f, rm = 0.f;
+    auto fetch = [&](int t0) {
+        const int nt = q_len - t0 < TT ? q_len - t0 : TT;
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const int idx = tid + e * THREADS;
+            int t = idx / (SLICES * RC), c = idx % (SLICES * RC);
+            t = t < nt ? t : nt - 1;
+            c = c < d ? c : d - 1;
+            const int64_t row = q_start + t0 + t;
+            const T* r = base + row * p.row_stride;
+            rq[e] = r[p.q_off + h * d + c];
+            rk[e] = r[p.k_off + h * d + c];
+            ra[e] = SCALAR ? p.coef[(row * H + h) * 4 + 1] : p.decay[row * p.decay_stride + h * d + c];
+        }
+        {
+            int t = tid / COLS, jj = j0 + tid % COLS;      // TT * COLS == THREADS
+            t = t < nt ? t : nt - 1;
+            jj = jj < dv ? jj : dv - 1;
+            rv = base[(int64_t)(q_start + t0 + t) * p.row_stride + p.v_off + h * dv + jj];
+        }
+        if (SCALAR) {
+            const int64_t row = q_start + t0 + (tid < nt ? tid : nt - 1);
+            rkeep = p.coef[(row * H + h) * 4];
+            rm = p.coef[(row * H + h) * 4 + 2];
+        }
+    };
+    if (q_len > 0) fetch(0);
     for (int t0 = 0; t0 < q_len; t0 += TT) {
         const int nt = q_len - t0 < TT ? q_len - t0 : TT;
         __syncthreads();   // the tile before is done with
-        // stage the tokens' rows: q scaled, k (times the input gate), the decays, this block's values
-        for (int idx = tid; idx < nt * SLICES * RC; idx += THREADS) {
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const int idx = tid + e * THREADS;
             const int t = idx / (SLICES * RC), c = idx % (SLICES * RC);
-            const int64_t row = q_start + t0 + t;
             const int at = (c / RC) * P + c % RC;
-            float qv = 0.f, kv = 0.f, av = 0.f;
-            if (c < d) {
-                const T* r = base + row * p.row_stride;
-                qv = to_f32<T>(r[p.q_off + h * d + c]) * p.q_scale;
-                kv = to_f32<T>(r[p.k_off + h * d + c]);
-                if (SCALAR)
-                    kv *= p.coef[(row * H + h) * 4 + 1];
-                else
-                    av = p.decay[row * p.decay_stride + h * d + c];
-            }
-            q_s[t][at] = qv;
-            k_s[t][at] = kv;
-            if (!SCALAR) a_s[t][at] = av;
+            const bool there = t < nt && c < d;
+            q_s[t][at] = there ? to_f32<T>(rq[e]) * p.q_scale : 0.f;
+            // one decay per head: the input gate goes into the key, the decay itself is keep_s
+            k_s[t][at] = there ? (SCALAR ? to_f32<T>(rk[e]) * ra[e] : to_f32<T>(rk[e])) : 0.f;
+            if (!SCALAR) a_s[t][at] = there ? ra[e] : 1.f;
         }
-        for (int idx = tid; idx < nt * COLS; idx += THREADS) {
-            const int t = idx / COLS, jj = idx % COLS;
-            const int64_t row = q_start + t0 + t;
+        {
+            const int t = tid / COLS, jj = tid % COLS;
             float v = 0.f;
-            if (norm_col)
-                v = jj == 0 ? 1.f : 0.f;
-            else if (j0 + jj < dv)
-                v = to_f32<T>(base[row * p.row_stride + p.v_off + h * dv + j0 + jj]);
+            if (t < nt) {
+                if (norm_col)
+                    v = jj == 0 ? 1.f : 0.f;
+                else if (j0 + jj < dv)
+                    v = to_f32<T>(rv);
+            }
             v_s[t][jj] = v;
         }
-        if (SCALAR && tid < nt) {
-            const int64_t row = q_start + t0 + tid;
-            keep_s[tid] = p.coef[(row * H + h) * 4];
-            m_s[tid] = p.coef[(row * H + h) * 4 + 2];
+        if (SCALAR && tid < TT) {
+            keep_s[tid] = tid < nt ? rkeep : 1.f;
+            m_s[tid] = rm;
         }
         __syncthreads();
-        for (int t = 0; t < nt; t++) {
+        if (t0 + TT < q_len) fetch(t0 + TT);
+        // All eight tokens of the tile, unrolled (a tile's missing tokens leave the state as it is: decay 1,
+        // key 0).  A thread's sums over its slice of the channels stay in registers until the tile is done;
+        // then three exchange steps add the eight slices up and leave token t's sum with the lane of slice t.
+        float acc[TT];
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
             const float vj = v_s[t][col];
             const float keep = SCALAR ? keep_s[t] : 0.f;
             float acc0 = 0.f, acc1 = 0.f, acc2 = 0.f, acc3 = 0.f;
@@ -188,12 +237,24 @@ __global__ void __launch_bounds__(THREADS) state_scan_kernel(LinearStateParams p
                 acc2 = fmaf(st[i + 2], q4.z, acc2);
                 acc3 = fmaf(st[i + 3], q4.w, acc3);
             }
-            float acc = (acc0 + acc1) + (acc2 + acc3);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (slice == 0) o_s[t][col] = acc;
+            acc[t] = (acc0 + acc1) + (acc2 + acc3);
         }
+        float b4[4], b2[2], total;
+        {
+            const bool up = slice & 4;
+#pragma unroll
+            for (int j = 0; j < 4; j++) b4[j] = (up ? acc[j + 4] : acc[j]) + __shfl_xor_sync(0xffffffffu, up ? acc[j] : acc[j + 4], 4);
+        }
+        {
+            const bool up = slice & 2;
+#pragma unroll
+            for (int j = 0; j < 2; j++) b2[j] = (up ? b4[j + 2] : b4[j]) + __shfl_xor_sync(0xffffffffu, up ? b4[j] : b4[j + 2], 2);
+        }
+        {
+            const bool up = slice & 1;
+            total = (up ? b2[1] : b2[0]) + __shfl_xor_sync(0xffffffffu, up ? b2[0] : b2[1], 1);
+        }
+        o_s[slice][col] = total;
         __syncthreads();
         if (norm_col) {
             // n . q of the tile's tokens -> the divisor max(|n . q|, exp(-m)) + 1e-6
@@ -212,7 +273,16 @@ __global__ void __launch_bounds__(THREADS) state_scan_kernel(LinearStateParams p
 #pragma unroll
     for (int i = 0; i < RC; i++) st_s[slice * RC + i][col] = st[i];
     __syncthreads();
-    for (int idx = tid; idx < SLICES * RC * COLS; idx += THREADS) {
+    if (vec) {
+#pragma unroll 4
+        for (int idx = tid; idx < SLICES * RC * (COLS / 4); idx += THREADS) {
+            const int c = idx / (COLS / 4), q4 = idx % (COLS / 4);
+            if (c < d)
+                *reinterpret_cast<float4*>(S + (int64_t)c * dv + j0 + 4 * q4) =
+                    make_float4(st_s[c][4 * q4], st_s[c][4 * q4 + 1], st_s[c][4 * q4 + 2], st_s[c][4 * q4 + 3]);
+        }
+    }
+    for (int idx = tid; !vec && idx < SLICES * RC * COLS; idx += THREADS) {
         const int c = idx / COLS, jj = idx % COLS;
         if (c >= d) continue;
         if (norm_col) {
@@ -223,8 +293,98 @@ __global__ void __launch_bounds__(THREADS) state_scan_kernel(LinearStateParams p
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// One token for every sequence (a decode step): the work is reading and writing the state once.  A CTA
+// owns 16 columns of one head's S; thread (group g of 8, column j of 16) takes the channels g, g + 8, ...
+// so that a warp's loads are whole 64-byte rows, keeps them in registers from load to store, and the
+// eight groups' sums meet in shared memory.  All state loads are issued before anything waits.
+template <typename T, int R, bool SCALAR>
+__global__ void __launch_bounds__(THREADS) state_step_kernel(LinearStateParams p) {
+    __shared__ float q_s[SLICES * R], k_s[SLICES * R], a_s[SLICES * R];
+    __shared__ float red[SLICES][COLS + 1];
+    const int tid = threadIdx.x, jj = tid & (COLS - 1), g = tid >> 4;
+    const int d = p.d, dv = p.dv, H = p.heads;
+    const int h = blockIdx.y, seq = blockIdx.z;
+    const int vblocks = (dv + COLS - 1) / COLS;
+    const bool norm_col = SCALAR && (int)blockIdx.x == vblocks;
+    const int j = blockIdx.x * COLS + jj;
+    const int64_t row = p.seq_q_start[seq];
+    int slot = p.seq_slot[seq];
+    if (!gb_check(slot, p.max_slots, GB_CHECK_SLOT)) slot = 0;
+    float* S = p.state + (int64_t)slot * p.slot_stride + (int64_t)h * p.head_stride;
+    float* nvec = S + (int64_t)d * dv;
+    const bool mine = norm_col ? jj == 0 : j < dv;
+
+    float st[R];
+#pragma unroll
+    for (int i = 0; i < R; i++) {
+        const int c = g + SLICES * i;
+        st[i] = (mine && c < d) ? (norm_col ? nvec[c] : S[(int64_t)c * dv + j]) : 0.f;
+    }
+    const T* r = (const T*)p.qkv + row * p.row_stride;
+    float keep = 0.f, take = 1.f, m = 0.f;
+    if (SCALAR) {
+        const float* cf = p.coef + (row * H + h) * 4;
+        keep = cf[0];
+        take = cf[1];
+        m = cf[2];
+    }
+    for (int c = tid; c < SLICES * R; c += THREADS) {
+        const bool there = c < d;
+        q_s[c] = there ? to_f32<T>(r[p.q_off + h * d + c]) * p.q_scale : 0.f;
+        k_s[c] = there ? to_f32<T>(r[p.k_off + h * d + c]) * take : 0.f;
+        a_s[c] = SCALAR ? keep : (there ? p.decay[row * p.decay_stride + h * d + c] : 1.f);
+    }
+    const float vj = norm_col ? 1.f : (j < dv ? to_f32<T>(r[p.v_off + h * dv + j]) : 0.f);
+    __syncthreads();
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < R; i++) {
+        const int c = g + SLICES * i;
+        st[i] = fmaf(a_s[c], st[i], k_s[c] * vj);
+        acc = fmaf(st[i], q_s[c], acc);
+    }
+#pragma unroll
+    for (int i = 0; i < R; i++) {
+        const int c = g + SLICES * i;
+        if (mine && c < d) {
+            if (norm_col)
+                nvec[c] = st[i];
+            else
+                S[(int64_t)c * dv + j] = st[i];
+        }
+    }
+    red[g][jj] = acc;
+    __syncthreads();
+    if (tid < COLS) {
+        float total = 0.f;
+#pragma unroll
+        for (int s = 0; s < SLICES; s++) total += red[s][tid];
+        if (norm_col) {
+            if (tid == 0) p.coef[(row * H + h) * 4 + 3] = fmaxf(fabsf(total), expf(-m)) + 1e-6f;
+        } else if (j < dv) {
+            p.out[row * p.out_stride + h * dv + j] = total;
+        }
+    }
+}
+
+template <typename T, bool SCALAR>
+int launch_step(const LinearStateParams& p, cudaStream_t stream) {
+    dim3 grid((p.dv + COLS - 1) / COLS + (SCALAR ? 1 : 0), p.heads, p.nseq);
+    if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("state_scan: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);
+    if (p.d <= 64)
+        state_step_kernel<T, 8, SCALAR><<<grid, THREADS, 0, stream>>>(p);
+    else if (p.d <= 128)
+        state_step_kernel<T, 16, SCALAR><<<grid, THREADS, 0, stream>>>(p);
+    else
+        state_step_kernel<T, 32, SCALAR><<<grid, THREADS, 0, stream>>>(p);
+    GB_CHECK_LAUNCH("state_step");
+    return 0;
+}
+
 template <typename T, bool SCALAR>
 int launch_scan(const LinearStateParams& p, cudaStream_t stream) {
+    if (p.max_q_len == 1) return launch_step<T, SCALAR>(p, stream);   // every sequence brings one token
     const int rc = ((p.d + SLICES - 1) / SLICES + 3) / 4 * 4;
     dim3 grid((p.dv + COLS - 1) / COLS + (SCALAR ? 1 : 0), p.heads, p.nseq);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("state_scan: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);

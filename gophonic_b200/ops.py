@@ -670,6 +670,7 @@ class _LinearStateParams(Structure):
         ("gate_cap", c_float), ("coef", c_void_p), ("state", c_void_p), ("slot_stride", c_int64), ("head_stride", c_int64),
         ("out", c_void_p), ("out_stride", c_int64), ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
         ("nseq", c_int), ("heads", c_int), ("d", c_int), ("dv", c_int), ("scalar_decay", c_int), ("max_slots", c_int),
+        ("max_q_len", c_int),
     ]
 
 
@@ -697,14 +698,17 @@ def gla_decay(z: torch.Tensor, bias: Optional[torch.Tensor], tau: float) -> None
 def state_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, d: int, dv: int, q_scale: float,
                state: torch.Tensor, out: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor, seq_q_len: torch.Tensor,
                nseq: int, decay: Optional[torch.Tensor] = None, gates: Optional[torch.Tensor] = None,
-               gate_bias: Optional[torch.Tensor] = None, gate_cap: float = 0.0, coef: Optional[torch.Tensor] = None) -> None:
+               gate_bias: Optional[torch.Tensor] = None, gate_cap: float = 0.0, coef: Optional[torch.Tensor] = None,
+               max_q_len: int = 0) -> None:
     """The matrix-state recurrence S <- diag(a) S + b k v^T, o = S^T (q * q_scale) over the rows of a step,
     token by token, for every (sequence, head); ``state`` [slots, heads, d * dv (+ d + 1)] float32 is read
     and left updated, ``out`` [rows, heads * dv] float32 receives the sums.  With ``decay`` (float32 [rows,
     heads * d]) a is a factor per key channel and b = 1.  With ``gates`` (float32 [rows, 2 * heads]: input
     then forget pre-activations), ``gate_bias``, ``gate_cap`` and ``coef`` (float32 [rows, heads, 4] scratch)
     a and b are the stabilised exponential gates of a matrix memory, the state also carries the
-    normaliser and the running maximum, and coef[..., 3] receives each token's divisor."""
+    normaliser and the running maximum, and coef[..., 3] receives each token's divisor.  ``max_q_len``:
+    the most rows a sequence brings, if known (1: every sequence brings one token, which has a kernel
+    of its own; the arithmetic per element is the same)."""
     _need(qkv, "state_scan rows", dim=2, contiguous=False)
     _need(state, "state", torch.float32, 3)
     _need(out, "state_scan out", torch.float32, 2)
@@ -740,7 +744,7 @@ def state_scan(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int
                            0 if gate_bias is None else gate_bias.data_ptr(), gate_cap, 0 if coef is None else coef.data_ptr(),
                            state.data_ptr(), state.stride(0), state.stride(1), out.data_ptr(), out.stride(0),
                            seq_slot.data_ptr(), seq_q_start.data_ptr(), seq_q_len.data_ptr(), nseq, heads, d, dv,
-                           1 if scalar else 0, state.shape[0])
+                           1 if scalar else 0, state.shape[0], int(max_q_len))
     _check(_lib.gb_state_scan(byref(p), _code(qkv.dtype), _stream()), 2 if scalar else 1)
 
 

@@ -97,7 +97,7 @@ class DecayState(_StateMixer):
         ops.gla_decay(decay, self.a_bias, float(s.tau))
         o = torch.empty((rows, self.vd), dtype=torch.float32, device=x.device)
         ops.state_scan(buf, 0, self.kd, 2 * self.kd, s.heads, s.key_dim, s.value_dim, self.q_scale, cache.state, o,
-                       batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.nseq, decay=decay)
+                       batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.nseq, decay=decay, max_q_len=batch.max_q_len)
         y = torch.empty((rows, self.vd), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(o, buf[:, self.g_off:self.g_off + self.vd], y, s.heads, s.value_dim, ops.GATE_SILU,
                            weight=self.norm_w, eps=float(s.eps))
@@ -109,7 +109,8 @@ class MatrixMemory(_StateMixer):
 
     @classmethod
     def extra_state_of(cls, spec) -> int:
-        return spec.key_dim + 1      # the normaliser and the running maximum
+        # the normaliser and the running maximum, rounded up so that every head's matrix starts on 16 bytes
+        return (spec.key_dim + 1 + 3) // 4 * 4
 
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
@@ -137,7 +138,7 @@ class MatrixMemory(_StateMixer):
         o = torch.empty((rows, self.vd), dtype=torch.float32, device=x.device)
         ops.state_scan(buf, 0, self.kd, 2 * self.kd, s.heads, s.key_dim, s.value_dim, self.q_scale, cache.state, o,
                        batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.nseq, gates=gates, gate_bias=self.gate_bias,
-                       gate_cap=float(s.gate_cap), coef=coef)
+                       gate_cap=float(s.gate_cap), coef=coef, max_q_len=batch.max_q_len)
         y = torch.empty((rows, self.vd), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(o, buf[:, self.g_off:self.g_off + self.vd], y, s.heads, s.value_dim, ops.GATE_SIGMOID,
                            weight=self.norm_w, eps=float(s.eps), divisor=coef[:, :, 3:])

@@ -200,6 +200,10 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
         if (lo_pos < 0) lo_pos = 0;
     }
     const int t_lo = lo_pos / BKV;
+    // with kept first tokens: the pages of keys [0, keep_first) first, then those of the window, each once
+    int n_first = p.window > 0 && p.keep_first > 0 ? (p.keep_first + BKV - 1) / BKV : 0;
+    if (n_first > t_lo) n_first = t_lo;
+    auto tile_of = [&](int j) { return j < n_first ? j : t_lo + (j - n_first); };
     int n_g[GROUPS];
 #pragma unroll
     for (int g = 0; g < GROUPS; g++) {
@@ -208,7 +212,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             n_g[g] = 0;
         } else {
             const int last = (first + BQ < q_len ? first + BQ : q_len) - 1;
-            n_g[g] = (past + last) / BKV - t_lo + 1;
+            n_g[g] = n_first + (past + last) / BKV - t_lo + 1;
         }
     }
     const int n = n_g[0] > n_g[1] ? n_g[0] : n_g[1];
@@ -264,7 +268,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 if (*(volatile int*)&abort_s) break;
                 mbar_expect_tx(&k_full[s], K_BYTES);
                 unsigned char* ks = KVs + (size_t)s * STAGE_BYTES;
-                int lp = t_lo + j;
+                int lp = tile_of(j);
                 if (!gb_check(lp, p.bt_stride, GB_CHECK_LOGICAL_PAGE) || lp >= p.bt_stride) lp = p.bt_stride - 1;
                 const int row = ((int)page_of(bt, lp * BKV, p.bt_stride, p.pages) * p.kv_heads + kvh) * 64;
 #pragma unroll
@@ -290,7 +294,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 if (*(volatile int*)&abort_s) break;
                 mbar_expect_tx(&v_full[s], V_BYTES);
                 unsigned char* vs = KVs + (size_t)s * STAGE_BYTES + K_BYTES;
-                int lp = t_lo + j;
+                int lp = tile_of(j);
                 if (!gb_check(lp, p.bt_stride, GB_CHECK_LOGICAL_PAGE) || lp >= p.bt_stride) lp = p.bt_stride - 1;
                 const int row = ((int)page_of(bt, lp * BKV, p.bt_stride, p.pages) * p.kv_heads + kvh) * 64;
 #pragma unroll
@@ -399,7 +403,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
         float l = 0.f;
         bool ok = true;
         for (int j = 0; j < my_n && ok; j++) {
-            const int b = j & 1, key0 = (t_lo + j) * BKV;
+            const int b = j & 1, key0 = tile_of(j) * BKV;
             if (!mbar_wait(&s_full[g][b], (uint32_t)(j >> 1) & 1u)) {
                 ok = false;
                 break;
@@ -416,8 +420,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     const int ka = key0 + i, kb = key0 + 32 + i;
-                    if (ka > pos || (p.window > 0 && ka <= pos - p.window)) v0[i] = 0xff800000u;  // -inf
-                    if (kb > pos || (p.window > 0 && kb <= pos - p.window)) v1[i] = 0xff800000u;
+                    if (ka > pos || (p.window > 0 && ka <= pos - p.window && ka >= p.keep_first)) v0[i] = 0xff800000u;  // -inf
+                    if (kb > pos || (p.window > 0 && kb <= pos - p.window && kb >= p.keep_first)) v1[i] = 0xff800000u;
                 }
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -499,6 +503,9 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             abort_s = 1;
         } else if (my_n > 0) {
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            // a sink adds one unit to the denominator: a key of score 0, in the scale the sums are kept in
+            // (a sum so scaled that the unit overflows gives 1 / inf = 0, which is the limit)
+            if (p.sink && m_used != -INFINITY) l += exp2f(-m_used);
             const float inv = 1.f / l;
             bf16* op = (bf16*)p.out + (int64_t)(q_start + qrow) * p.out_row_stride + (int64_t)head * HD;
 #pragma unroll 1
@@ -557,8 +564,8 @@ GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, c
     if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("%s: %d heads over %d kv heads", who, p.heads, p.kv_heads);
     if (p.num_splits != 1) GB_REFUSE("%s: key splits are for single-token rows", who);
     if (p.window < 0) GB_REFUSE("%s: window %d", who, p.window);
-    if ((p.dv && p.dv != p.d) || p.keep_first || p.sink)
-        GB_REFUSE("%s: values of another size than keys, kept first tokens and a sink run on the CUDA-core kernel", who);
+    if (p.dv && p.dv != p.d) GB_REFUSE("%s: values of another size than keys run on the CUDA-core kernel", who);
+    if (p.keep_first < 0) GB_REFUSE("%s: %d kept first tokens", who, p.keep_first);
     if (((uintptr_t)p.q & 15) || (p.q_row_stride & 7)) GB_REFUSE("%s: query rows must be 16-byte aligned", who);
     if (((uintptr_t)p.out & 15) || (p.out_row_stride & 7)) GB_REFUSE("%s: output rows must be 16-byte aligned", who);
     if (((uintptr_t)p.k_plane & 15) || ((uintptr_t)p.v_plane & 15)) GB_REFUSE("%s: cache planes must be 16-byte aligned", who);

@@ -51,7 +51,9 @@ CONFIGS = {
     # grouped heads, a window shorter and longer than a page
     "tensor": config([attention(heads=4, kv_heads=2, dim=32, vdim=32, rot=8, size=40, keep=2, ff=64), mlstm(heads=2, dim=16, vdim=16),
                       attention(heads=6, kv_heads=2, dim=64, vdim=64, rot=64, size=100, keep=70, scale=0.1),
-                      attention(heads=6, kv_heads=2, dim=64, vdim=64, rot=64, size=7, keep=1, scale=0.1, kv_from=2)], width=96, vocab=80),
+                      attention(heads=6, kv_heads=2, dim=64, vdim=64, rot=64, size=7, keep=1, scale=0.1, kv_from=2),
+                      # heads of 128: prompts of 65 rows and more run on the tcgen05 attention kernel
+                      attention(heads=2, kv_heads=1, dim=128, vdim=128, rot=32, size=70, keep=3, scale=0.09)], width=96, vocab=80),
     # sizes that are odd, equal, or 1: one head everywhere, key and value sizes equal in attention and not
     # multiples of 8 elsewhere, the whole head rotated, more kept tokens than the window is long
     "odd": config([attention(heads=1, kv_heads=1, dim=24, vdim=24, rot=24, size=5, keep=8, scale=0.31, ff=56),

@@ -26,7 +26,7 @@ def _ids(text: str):
 
 def main(argv=None) -> int:
     from .config.presets import preset_names
-    ap = argparse.ArgumentParser(prog="gophonic_b200", description="generate from a Qwen3 model folder")
+    ap = argparse.ArgumentParser(prog="gophonic_b200", description="generate from a model folder (Qwen3 or Pugalix)")
     ap.add_argument("-model", "--model", default="", help="model: a checkpoint directory (config.json, model.safetensors)")
     ap.add_argument("-random-config", "--random-config", default="", choices=[""] + preset_names(),
                     help="instead of -model: a named configuration with seeded random weights")

@@ -423,6 +423,40 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(HeadGateParams p) {
     const T* g = (const T*)p.gate + r * p.gate_stride + (int64_t)h * n;
     T* y = (T*)p.y + r * p.y_stride + (int64_t)h * n;
     const float div = p.divisor ? p.divisor[(r * p.heads + h) * p.divisor_stride] : 1.f;
+    const float* w = p.weight ? p.weight + (p.weight_per_head ? (int64_t)h * n : 0) : nullptr;
+    // heads of up to 256: every lane keeps its elements in registers, so x is read once and all of a
+    // lane's loads (x, gate, weight) are in flight together
+    if (n <= 256) {
+        float v[8], z[8], ww[8];
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int i = lane + 32 * e;
+            const bool in = i < n;
+            v[e] = in ? to_f32<TI>(x[i]) : 0.f;
+            z[e] = in ? to_f32<T>(g[i]) : 0.f;
+            ww[e] = (in && w) ? w[i] : 1.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            if (p.divisor) v[e] /= div;
+            ss += v[e] * v[e];
+        }
+        float inv = 1.f;
+        if (p.normed) inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + p.eps);
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const int i = lane + 32 * e;
+            if (i >= n) continue;
+            float o = v[e];
+            if (p.normed) o *= inv;
+            if (w) o *= ww[e];
+            const float sg = 1.f / (1.f + expf(-z[e]));
+            o *= p.gate_kind == 1 ? z[e] * sg : sg;
+            y[i] = from_f32<T>(o);
+        }
+        return;
+    }
     float ss = 0.f;
     if (p.normed) {
         for (int i = lane; i < n; i += 32) {
@@ -432,7 +466,6 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(HeadGateParams p) {
         ss = warp_sum(ss);
     }
     const float inv = p.normed ? 1.0f / sqrtf(ss / (float)n + p.eps) : 1.f;
-    const float* w = p.weight ? p.weight + (p.weight_per_head ? (int64_t)h * n : 0) : nullptr;
     for (int i = lane; i < n; i += 32) {
         float v = to_f32<TI>(x[i]);
         if (p.divisor) v /= div;

@@ -76,9 +76,18 @@ class GatedAttention(Attention):
         self.o_dim = spec.heads * spec.value_dim
         self.g_off = self.q_dim + self.k_dim + self.v_dim
 
-    # the folded and in-place paths of the plain attention part are not offered
+    # prompt-sized steps: the output projection adds into the float32 residual in its own epilogue
+    # (the folded decode path of the plain attention part is not offered)
     def adds_in_place(self, rows: int) -> bool:
-        return False
+        ops = self.rt.ops
+        return (self.o.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16 and self.o_dim % 8 == 0
+                and self.spec.hidden % 4 == 0 and ops.gemm_algo(rows, self.spec.hidden, self.o_dim) == "tc5_pair")
+
+    def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor, cache) -> None:
+        self.rt.ops.gemm_add(self._gated_heads(batch, x, cache), self.o, h)
+
+    def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
+        self.rt.ops.gemm(self._gated_heads(batch, x, cache), self.o, out)
 
     def folds_norm(self, rows: int, norm) -> bool:
         return False
@@ -99,7 +108,8 @@ class GatedAttention(Attention):
         return splits, batch.workspace(("attention key splits", s.heads, s.value_dim, splits),
                                        self.rt.ops.attention_scratch_floats(batch.nseq, s.heads, s.value_dim, splits))
 
-    def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
+    def _gated_heads(self, batch, x: torch.Tensor, cache) -> torch.Tensor:
+        """Everything up to the output projection: [rows, heads * value_dim] in the activation dtype."""
         ops, s = self.rt.ops, self.spec
         rows = x.shape[0]
         if cache is None:
@@ -122,4 +132,4 @@ class GatedAttention(Attention):
                       splits, scratch, value_dim=s.value_dim, keep_first=int(s.keep_first), sink=bool(s.sink))
         if s.gate:
             ops.head_norm_gate(ctx, qkvg[:, self.g_off:self.g_off + self.o_dim], ctx, s.heads, s.value_dim, ops.GATE_SIGMOID)
-        ops.gemm(ctx, self.o, out)
+        return ctx

@@ -55,6 +55,18 @@ class _StateMixer(Mixer):
     def weight_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._matrices())
 
+    # prompt-sized steps: the output projection adds into the float32 residual in its own epilogue
+    def adds_in_place(self, rows: int) -> bool:
+        ops = self.rt.ops
+        return (self.o.dtype == torch.bfloat16 and self.rt.act_dtype == torch.bfloat16 and self.vd % 8 == 0
+                and self.spec.hidden % 4 == 0 and ops.gemm_algo(rows, self.spec.hidden, self.vd) == "tc5_pair")
+
+    def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
+        self.rt.ops.gemm(self._heads(batch, x, cache), self.o, out)
+
+    def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor, cache) -> None:
+        self.rt.ops.gemm_add(self._heads(batch, x, cache), self.o, h)
+
     def _project(self, x):
         rows = x.shape[0]
         buf = torch.empty((rows, self.qkvg.shape[0]), dtype=x.dtype, device=x.device)
@@ -85,7 +97,8 @@ class DecayState(_StateMixer):
     def _matrices(self):
         return (self.qkvg, self.o, self.a1, self.a2)
 
-    def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
+    def _heads(self, batch, x: torch.Tensor, cache) -> torch.Tensor:
+        """Everything up to the output projection: the normed and gated heads, [rows, heads * value_dim]."""
         ops, s = self.rt.ops, self.spec
         rows = x.shape[0]
         buf = self._project(x)
@@ -101,7 +114,7 @@ class DecayState(_StateMixer):
         y = torch.empty((rows, self.vd), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(o, buf[:, self.g_off:self.g_off + self.vd], y, s.heads, s.value_dim, ops.GATE_SILU,
                            weight=self.norm_w, eps=float(s.eps))
-        ops.gemm(y, self.o, out)
+        return y
 
 
 class MatrixMemory(_StateMixer):
@@ -128,7 +141,7 @@ class MatrixMemory(_StateMixer):
     def _matrices(self):
         return (self.qkvg, self.o, self.gates_w)
 
-    def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
+    def _heads(self, batch, x: torch.Tensor, cache) -> torch.Tensor:
         ops, s = self.rt.ops, self.spec
         rows = x.shape[0]
         buf = self._project(x)
@@ -142,4 +155,4 @@ class MatrixMemory(_StateMixer):
         y = torch.empty((rows, self.vd), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(o, buf[:, self.g_off:self.g_off + self.vd], y, s.heads, s.value_dim, ops.GATE_SIGMOID,
                            weight=self.norm_w, eps=float(s.eps), divisor=coef[:, :, 3:])
-        ops.gemm(y, self.o, out)
+        return y

@@ -117,7 +117,7 @@ TOL = {"float32": 3e-5, "bfloat16": 6e-2}
 @pytest.mark.parametrize("name", ["attention", "gla", "mlstm", "mix", "odd", "tensor"])
 def test_whole_prompts_match_the_plain_model(models, name, dtype):
     cfg, w, _ = models[name]
-    toks = tokens_for(cfg, 1, 230 if name == "tensor" else 150)
+    toks = tokens_for(cfg, 1, 230)      # from 192 rows on the output projections add into the residual themselves
     close(feed(engine_for(models, name, dtype), toks), P.forward(cfg, w, toks), TOL[dtype])
 
 

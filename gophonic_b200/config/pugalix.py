@@ -89,7 +89,7 @@ class PugalixConfig:
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "PugalixConfig":
         width, vocab = _int(d, "width", ""), _int(d, "vocab", "")
-        scale = _pos(_get(d, "embedding", ""), "scale", "embedding.")
+        scale = _pos(d["embedding"], "scale", "embedding.") if isinstance(d.get("embedding"), dict) else 1.0
         eps = _pos(_get(d, "norm", ""), "eps", "norm.")
         raw_layers = _get(d, "layers", "")
         if not isinstance(raw_layers, list) or not raw_layers:
@@ -104,8 +104,21 @@ class PugalixConfig:
             if not isinstance(m, dict):
                 raise ConfigError(f"config.json: '{at}mixer' must be an object")
             ma = at + "mixer."
-            _int(m, "heads", ma), _int(m, "dim", ma), _int(m, "vdim", ma)
+            m = dict(m)
+            _int(m, "heads", ma), _int(m, "dim", ma)
+            if m.get("vdim") is None:
+                m["vdim"] = m["dim"]                 # values as wide as keys unless the file says otherwise
+            _int(m, "vdim", ma)
             if kind == "attention":
+                # what a file leaves out is not there: no grouping, no rotation, no window
+                if m.get("kv_heads") is None:
+                    m["kv_heads"] = m["heads"]
+                if m.get("rot") is None:
+                    m["rot"] = {"dims": 0, "base": 10000.0}
+                if m.get("mask") is None:
+                    m["mask"] = {"size": _LIMIT, "keep_first": 0}
+                elif isinstance(m["mask"], dict) and m["mask"].get("keep_first") is None:
+                    m["mask"] = dict(m["mask"], keep_first=0)
                 heads, kvh = m["heads"], _int(m, "kv_heads", ma)
                 if heads % kvh:
                     raise ConfigError(f"config.json: '{ma}heads' {heads} is not a multiple of '{ma}kv_heads' {kvh}")

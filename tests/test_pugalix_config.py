@@ -52,6 +52,19 @@ def test_a_rank_in_the_file_is_taken_and_random_weights_need_it(tmp_path):
     assert {n: tuple(a.shape) for n, a in w.items()} == P.tensor_shapes(cfg)
 
 
+def test_what_a_file_leaves_out_of_an_attention_mixer_is_not_there():
+    from gophonic_b200.config import PugalixConfig
+    cfg = copy.deepcopy(CONFIGS["attention"])
+    m = cfg["layers"][0]["mixer"]
+    for key in ("kv_heads", "rot", "mask", "vdim"):
+        m.pop(key)
+    cfg.pop("embedding")
+    spec = PugalixConfig.from_dict(cfg).model_spec()
+    a = spec.layers[0].mixer
+    assert a.kv_heads == a.heads and a.value_dim == a.head_dim and a.position.rotary_dim == 0 and a.keep_first == 0
+    assert a.window >= 1 << 20 and spec.embedding.scale == 1.0          # a window no sequence reaches
+
+
 def test_the_schedule_shares_a_cache_plane_and_layers_may_lack_a_feed_forward():
     from gophonic_b200.config import PugalixConfig
     spec = PugalixConfig.from_dict(CONFIGS["mix"]).model_spec()

@@ -294,6 +294,214 @@ __global__ void __launch_bounds__(THREADS) state_scan_kernel(LinearStateParams p
 }
 
 // ------------------------------------------------------------------------------------------
+// The same scan for heads of 128 or 256 key channels, laid out so that shared memory is read once: a
+// warp owns 4 columns and its 32 lanes are 32 slices of the channels (RC = d / 32 each), a thread keeps
+// RC x 4 state elements.  A token's q, k and decay rows are then read by the warp as whole rows (every
+// lane its own 16 bytes, no two quarter-warps the same bytes), four times less shared-memory traffic
+// than with 8 slices and a column a thread, for the same registers.  A tile's 8 tokens x 4 columns of
+// sums are added up over the 32 slices by a five-step exchange that leaves each lane one of them.
+template <typename T, int RC, bool SCALAR>
+__global__ void __launch_bounds__(THREADS) state_scan_wide_kernel(LinearStateParams p) {
+    constexpr int D = 32 * RC;          // key channels of a head
+    constexpr int CW = 4;               // columns a warp (and a thread) owns
+    __shared__ __align__(16) float q_s[TT][D];
+    __shared__ __align__(16) float k_s[TT][D];
+    __shared__ __align__(16) float a_s[SCALAR ? 1 : TT][SCALAR ? 4 : D];
+    __shared__ __align__(16) float v_s[TT][COLS];
+    __shared__ float o_s[TT][COLS];
+    __shared__ float keep_s[TT], m_s[TT];
+    __shared__ float st_s[D][COLS + 1];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int dv = p.dv, H = p.heads;
+    const int h = blockIdx.y, seq = blockIdx.z;
+    const int vblocks = (dv + COLS - 1) / COLS;
+    const bool norm_col = SCALAR && (int)blockIdx.x == vblocks;
+    const int j0 = blockIdx.x * COLS;
+    const int q_len = p.seq_q_len[seq], q_start = p.seq_q_start[seq];
+    int slot = p.seq_slot[seq];
+    if (!gb_check(slot, p.max_slots, GB_CHECK_SLOT)) slot = 0;
+    float* S = p.state + (int64_t)slot * p.slot_stride + (int64_t)h * p.head_stride;
+    float* nvec = S + (int64_t)D * dv;
+
+    const bool vec = !norm_col && !(dv & 3) && j0 + COLS <= dv && !((uintptr_t)(S + j0) & 15);
+    if (vec) {
+#pragma unroll 4
+        for (int idx = tid; idx < D * (COLS / 4); idx += THREADS) {
+            const int c = idx / (COLS / 4), q4 = idx % (COLS / 4);
+            const float4 v = *reinterpret_cast<const float4*>(S + (int64_t)c * dv + j0 + 4 * q4);
+            st_s[c][4 * q4] = v.x;
+            st_s[c][4 * q4 + 1] = v.y;
+            st_s[c][4 * q4 + 2] = v.z;
+            st_s[c][4 * q4 + 3] = v.w;
+        }
+    }
+    for (int idx = tid; !vec && idx < D * COLS; idx += THREADS) {
+        const int c = idx / COLS, jj = idx % COLS;
+        float v = 0.f;
+        if (norm_col)
+            v = jj == 0 ? nvec[c] : 0.f;
+        else if (j0 + jj < dv)
+            v = S[(int64_t)c * dv + j0 + jj];
+        st_s[c][jj] = v;
+    }
+    __syncthreads();
+    float st[RC][CW];
+#pragma unroll
+    for (int i = 0; i < RC; i++)
+#pragma unroll
+        for (int c = 0; c < CW; c++) st[i][c] = st_s[lane * RC + i][warp * CW + c];
+
+    const T* base = (const T*)p.qkv;
+    constexpr int PER = TT * D / THREADS;
+    T rq[PER], rk[PER], rv;
+    float ra[PER], rkeep = 1.f, rm = 0.f;
+    auto fetch = [&](int t0) {
+        const int nt = q_len - t0 < TT ? q_len - t0 : TT;
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const int idx = tid + e * THREADS;
+            int t = idx / D;
+            const int c = idx % D;
+            t = t < nt ? t : nt - 1;
+            const int64_t row = q_start + t0 + t;
+            const T* r = base + row * p.row_stride;
+            rq[e] = r[p.q_off + h * D + c];
+            rk[e] = r[p.k_off + h * D + c];
+            ra[e] = SCALAR ? p.coef[(row * H + h) * 4 + 1] : p.decay[row * p.decay_stride + h * D + c];
+        }
+        {
+            int t = tid / COLS, jj = j0 + tid % COLS;
+            t = t < nt ? t : nt - 1;
+            jj = jj < dv ? jj : dv - 1;
+            rv = base[(int64_t)(q_start + t0 + t) * p.row_stride + p.v_off + h * dv + jj];
+        }
+        if (SCALAR) {
+            const int64_t row = q_start + t0 + (tid < nt ? tid : nt - 1);
+            rkeep = p.coef[(row * H + h) * 4];
+            rm = p.coef[(row * H + h) * 4 + 2];
+        }
+    };
+    if (q_len > 0) fetch(0);
+    for (int t0 = 0; t0 < q_len; t0 += TT) {
+        const int nt = q_len - t0 < TT ? q_len - t0 : TT;
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < PER; e++) {
+            const int idx = tid + e * THREADS;
+            const int t = idx / D, c = idx % D;
+            const bool there = t < nt;
+            q_s[t][c] = there ? to_f32<T>(rq[e]) * p.q_scale : 0.f;
+            k_s[t][c] = there ? (SCALAR ? to_f32<T>(rk[e]) * ra[e] : to_f32<T>(rk[e])) : 0.f;
+            if (!SCALAR) a_s[t][c] = there ? ra[e] : 1.f;
+        }
+        {
+            const int t = tid / COLS, jj = tid % COLS;
+            float v = 0.f;
+            if (t < nt) {
+                if (norm_col)
+                    v = jj == 0 ? 1.f : 0.f;
+                else if (j0 + jj < dv)
+                    v = to_f32<T>(rv);
+            }
+            v_s[t][jj] = v;
+        }
+        if (SCALAR && tid < TT) {
+            keep_s[tid] = tid < nt ? rkeep : 1.f;
+            m_s[tid] = rm;
+        }
+        __syncthreads();
+        if (t0 + TT < q_len) fetch(t0 + TT);
+        float acc[TT * CW];     // index t * 4 + c
+#pragma unroll
+        for (int t = 0; t < TT; t++) {
+            const float4 v4 = *reinterpret_cast<const float4*>(&v_s[t][warp * CW]);
+            const float vv[CW] = {v4.x, v4.y, v4.z, v4.w};
+            const float keep = SCALAR ? keep_s[t] : 0.f;
+            float sum[CW] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < RC; i += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(&q_s[t][lane * RC + i]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&k_s[t][lane * RC + i]);
+                float4 a4 = make_float4(keep, keep, keep, keep);
+                if (!SCALAR) a4 = *reinterpret_cast<const float4*>(&a_s[t][lane * RC + i]);
+                const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+#pragma unroll
+                    for (int c = 0; c < CW; c++) {
+                        st[i + u][c] = fmaf(aa[u], st[i + u][c], kk[u] * vv[c]);
+                        sum[c] = fmaf(st[i + u][c], qq[u], sum[c]);
+                    }
+            }
+#pragma unroll
+            for (int c = 0; c < CW; c++) acc[t * CW + c] = sum[c];
+        }
+        // 32 sums a thread over 32 slices: halve the sums and the lanes five times
+        float b16[16], b8[8], b4[4], b2[2], total;
+        {
+            const bool up = lane & 16;
+#pragma unroll
+            for (int j = 0; j < 16; j++) b16[j] = (up ? acc[j + 16] : acc[j]) + __shfl_xor_sync(0xffffffffu, up ? acc[j] : acc[j + 16], 16);
+        }
+        {
+            const bool up = lane & 8;
+#pragma unroll
+            for (int j = 0; j < 8; j++) b8[j] = (up ? b16[j + 8] : b16[j]) + __shfl_xor_sync(0xffffffffu, up ? b16[j] : b16[j + 8], 8);
+        }
+        {
+            const bool up = lane & 4;
+#pragma unroll
+            for (int j = 0; j < 4; j++) b4[j] = (up ? b8[j + 4] : b8[j]) + __shfl_xor_sync(0xffffffffu, up ? b8[j] : b8[j + 4], 4);
+        }
+        {
+            const bool up = lane & 2;
+#pragma unroll
+            for (int j = 0; j < 2; j++) b2[j] = (up ? b4[j + 2] : b4[j]) + __shfl_xor_sync(0xffffffffu, up ? b4[j] : b4[j + 2], 2);
+        }
+        {
+            const bool up = lane & 1;
+            total = (up ? b2[1] : b2[0]) + __shfl_xor_sync(0xffffffffu, up ? b2[0] : b2[1], 1);
+        }
+        o_s[lane >> 2][warp * CW + (lane & 3)] = total;     // lane l is left with sum number l = t * 4 + c
+        __syncthreads();
+        if (norm_col) {
+            if (tid < nt) {
+                const int64_t row = q_start + t0 + tid;
+                p.coef[(row * H + h) * 4 + 3] = fmaxf(fabsf(o_s[tid][0]), expf(-m_s[tid])) + 1e-6f;
+            }
+        } else {
+            for (int idx = tid; idx < nt * COLS; idx += THREADS) {
+                const int t = idx / COLS, jj = idx % COLS;
+                if (j0 + jj < dv) p.out[(int64_t)(q_start + t0 + t) * p.out_stride + h * dv + j0 + jj] = o_s[t][jj];
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < RC; i++)
+#pragma unroll
+        for (int c = 0; c < CW; c++) st_s[lane * RC + i][warp * CW + c] = st[i][c];
+    __syncthreads();
+    if (vec) {
+#pragma unroll 4
+        for (int idx = tid; idx < D * (COLS / 4); idx += THREADS) {
+            const int c = idx / (COLS / 4), q4 = idx % (COLS / 4);
+            *reinterpret_cast<float4*>(S + (int64_t)c * dv + j0 + 4 * q4) =
+                make_float4(st_s[c][4 * q4], st_s[c][4 * q4 + 1], st_s[c][4 * q4 + 2], st_s[c][4 * q4 + 3]);
+        }
+    }
+    for (int idx = tid; !vec && idx < D * COLS; idx += THREADS) {
+        const int c = idx / COLS, jj = idx % COLS;
+        if (norm_col) {
+            if (jj == 0) nvec[c] = st_s[c][0];
+        } else if (j0 + jj < dv) {
+            S[(int64_t)c * dv + j0 + jj] = st_s[c][jj];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // One token for every sequence (a decode step): the work is reading and writing the state once.  A CTA
 // owns 16 columns of one head's S; thread (group g of 8, column j of 16) takes the channels g, g + 8, ...
 // so that a warp's loads are whole 64-byte rows, keeps them in registers from load to store, and the
@@ -388,6 +596,14 @@ int launch_scan(const LinearStateParams& p, cudaStream_t stream) {
     const int rc = ((p.d + SLICES - 1) / SLICES + 3) / 4 * 4;
     dim3 grid((p.dv + COLS - 1) / COLS + (SCALAR ? 1 : 0), p.heads, p.nseq);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("state_scan: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);
+    if (p.d == 128 || p.d == 256) {     // heads whose channels fill a warp's 32 slices: shared memory read once
+        if (p.d == 128)
+            state_scan_wide_kernel<T, 4, SCALAR><<<grid, THREADS, 0, stream>>>(p);
+        else
+            state_scan_wide_kernel<T, 8, SCALAR><<<grid, THREADS, 0, stream>>>(p);
+        GB_CHECK_LAUNCH("state_scan");
+        return 0;
+    }
     switch (rc) {
         case 4: state_scan_kernel<T, 4, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;
         case 8: state_scan_kernel<T, 8, SCALAR><<<grid, THREADS, 0, stream>>>(p); break;

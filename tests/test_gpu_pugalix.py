@@ -54,6 +54,9 @@ CONFIGS = {
                       attention(heads=6, kv_heads=2, dim=64, vdim=64, rot=64, size=7, keep=1, scale=0.1, kv_from=2),
                       # heads of 128: prompts of 65 rows and more run on the tcgen05 attention kernel
                       attention(heads=2, kv_heads=1, dim=128, vdim=128, rot=32, size=70, keep=3, scale=0.09)], width=96, vocab=80),
+    # heads of 128 and 256 key channels: the scan kernel in which a warp's lanes are 32 slices of the channels
+    "wide": config([gla(heads=1, dim=128, vdim=24, tau=4.0), mlstm(heads=2, dim=128, vdim=16), gla(heads=1, dim=256, vdim=8, tau=2.0),
+                    mlstm(heads=1, dim=256, vdim=20, cap=8.0, ff=48)], width=64, vocab=70),
     # sizes that are odd, equal, or 1: one head everywhere, key and value sizes equal in attention and not
     # multiples of 8 elsewhere, the whole head rotated, more kept tokens than the window is long
     "odd": config([attention(heads=1, kv_heads=1, dim=24, vdim=24, rot=24, size=5, keep=8, scale=0.31, ff=56),
@@ -114,7 +117,7 @@ TOL = {"float32": 3e-5, "bfloat16": 6e-2}
 
 # ---- each mechanism alone, and all together ---------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["attention", "gla", "mlstm", "mix", "odd", "tensor"])
+@pytest.mark.parametrize("name", ["attention", "gla", "mlstm", "mix", "odd", "tensor", "wide"])
 def test_whole_prompts_match_the_plain_model(models, name, dtype):
     cfg, w, _ = models[name]
     toks = tokens_for(cfg, 1, 230)      # from 192 rows on the output projections add into the residual themselves
@@ -146,7 +149,7 @@ def test_the_residual_after_every_layer(models):
 
 # ---- prompts against decoding, portions, batches ----------------------------------------------
 @pytest.mark.parametrize("graphs", [True, False])
-@pytest.mark.parametrize("name", ["mix", "odd"])
+@pytest.mark.parametrize("name", ["mix", "odd", "wide"])
 def test_token_by_token_equals_the_whole_prompt(models, name, graphs):
     cfg, w, _ = models[name]
     eng = engine_for(models, name, "float32", graphs=graphs)
@@ -158,7 +161,7 @@ def test_token_by_token_equals_the_whole_prompt(models, name, graphs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mix", "tensor"])
+@pytest.mark.parametrize("name", ["mix", "tensor", "wide"])
 @pytest.mark.parametrize("cuts", [[2] * 40, [3, 64, 1, 2, 61], [63, 1, 1, 64], [130, 2]])
 def test_portions_of_a_prompt(models, cuts, dtype, name):
     cfg, w, _ = models[name]

@@ -57,6 +57,12 @@ CONFIGS = {
     # heads of 128 and 256 key channels: the scan kernel in which a warp's lanes are 32 slices of the channels
     "wide": config([gla(heads=1, dim=128, vdim=24, tau=4.0), mlstm(heads=2, dim=128, vdim=16), gla(heads=1, dim=256, vdim=8, tau=2.0),
                     mlstm(heads=1, dim=256, vdim=20, cap=8.0, ff=48)], width=64, vocab=70),
+    # attention first, one kv head for four heads, two later layers reading the first one's keys with
+    # masks of their own, and an attention layer of another head size with a cache group of its own
+    "shared": config([attention(heads=4, kv_heads=1, dim=16, vdim=32, rot=4, size=30, keep=2, ff=64), gla(ff=72),
+                      attention(heads=4, kv_heads=1, dim=16, vdim=32, rot=4, size=8, keep=0, kv_from=0), mlstm(ff=40),
+                      attention(heads=4, kv_heads=1, dim=16, vdim=32, rot=4, size=200, keep=5, kv_from=0, ff=64),
+                      attention(heads=2, kv_heads=2, dim=48, vdim=48, rot=48, size=16, keep=1, scale=0.14)], width=72, vocab=90),
     # sizes that are odd, equal, or 1: one head everywhere, key and value sizes equal in attention and not
     # multiples of 8 elsewhere, the whole head rotated, more kept tokens than the window is long
     "odd": config([attention(heads=1, kv_heads=1, dim=24, vdim=24, rot=24, size=5, keep=8, scale=0.31, ff=56),
@@ -117,7 +123,7 @@ TOL = {"float32": 3e-5, "bfloat16": 6e-2}
 
 # ---- each mechanism alone, and all together ---------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["attention", "gla", "mlstm", "mix", "odd", "tensor", "wide"])
+@pytest.mark.parametrize("name", ["attention", "gla", "mlstm", "mix", "odd", "tensor", "wide", "shared"])
 def test_whole_prompts_match_the_plain_model(models, name, dtype):
     cfg, w, _ = models[name]
     toks = tokens_for(cfg, 1, 230)      # from 192 rows on the output projections add into the residual themselves
@@ -149,7 +155,7 @@ def test_the_residual_after_every_layer(models):
 
 # ---- prompts against decoding, portions, batches ----------------------------------------------
 @pytest.mark.parametrize("graphs", [True, False])
-@pytest.mark.parametrize("name", ["mix", "odd", "wide"])
+@pytest.mark.parametrize("name", ["mix", "odd", "wide", "shared"])
 def test_token_by_token_equals_the_whole_prompt(models, name, graphs):
     cfg, w, _ = models[name]
     eng = engine_for(models, name, "float32", graphs=graphs)
@@ -338,13 +344,14 @@ def test_the_sink_matters_and_is_applied():
 
 
 # ---- the small kernels by themselves ------------------------------------------------------------
-def test_head_norm_gate_and_decay_kernels():
+@pytest.mark.parametrize("size", [20, 128, 384])      # heads of whole 128s take 16 bytes a lane
+def test_head_norm_gate_and_decay_kernels(size):
     import torch
     from gophonic_b200 import ops
     ops.use_device(0)
     dev = torch.device("cuda:0")
     rng = np.random.default_rng(0)
-    rows, heads, size = 7, 3, 20
+    rows, heads = 7, 3
     x = rng.standard_normal((rows, heads * size))
     g = rng.standard_normal((rows, heads * size))
     div = 0.5 + rng.random((rows, heads, 4))

@@ -34,6 +34,11 @@ struct AttnParams {
     float* scratch;  // [nseq][heads][num_splits][d + 2] when num_splits > 1
     int pages;       // pages of each cache plane, and slots (rows) of the block table: the bounds the
     int max_slots;   // checked build holds every page and slot index against
+};
+
+// The same with the options that came later.  AttnParams keeps its layout for callers that fill it
+// themselves; the entry points ending in _x take this one (the others behave as if the options were 0).
+struct AttnParamsX : AttnParams {
     int dv;          // size of a value head; 0: the same as d.  Only the CUDA-core kernel takes another size.
     int keep_first;  // with a window: keys at positions below this stay visible however far back they lie
     int sink;        // 1: the softmax denominator carries one more unit (a key of score 0 without a value)
@@ -61,7 +66,10 @@ struct QkRopeParams {
     int rows, heads, kv_heads, d;
     int pages;      // pages of each cache plane, and slots (rows) of the block table: the bounds the
     int max_slots;  // checked build holds every page and slot index against
-    // what only the general kernel takes (null / 0: absent)
+};
+
+// The same with what only the general kernel takes (null / 0: absent); QkRopeParams keeps its layout.
+struct QkRopeParamsX : QkRopeParams {
     const float* q_b;  // biases added to the heads before norm and rotation: [heads * d], [kv_heads * d], [kv_heads * dv]
     const float* k_b;
     const float* v_b;
@@ -120,6 +128,7 @@ GB_API int gb_add_rmsnorm(float* h, const float* delta, const float* w, float ep
                           int out_rows, cudaStream_t stream);
 GB_API int gb_swiglu(const void* gu, void* out, int dtype, int rows, int inter, int interleave8, cudaStream_t stream);
 GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* p, int dtype, cudaStream_t stream);
+GB_API int gb_qk_norm_rope_kv_write_x(const QkRopeParamsX* p, int dtype, cudaStream_t stream);
 
 // matrix products: C[M, N] = A[M, K] W[N, K]^T
 GB_API int gb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype, int M, int N, int K, int64_t lda,
@@ -148,6 +157,19 @@ GB_API int gb_attention_prefill_mma(const AttnParams* p, cudaStream_t stream);
 GB_API int gb_attention_decode_rope_accepts(int dtype, int d, int rot, int max_q_len);
 GB_API int gb_attention_decode_mma_rope(const AttnParams* p, const QkRopeParams* r, cudaStream_t stream);
 GB_API int gb_attention_prefill_tc5(const AttnParams* p, int rows, int pages, cudaStream_t stream);
+GB_API int gb_attention_simt_x(const AttnParamsX* p, int dtype, cudaStream_t stream);
+GB_API int gb_attention_decode_mma_x(const AttnParamsX* p, cudaStream_t stream);
+GB_API int gb_attention_prefill_mma_x(const AttnParamsX* p, cudaStream_t stream);
+GB_API int gb_attention_prefill_tc5_x(const AttnParamsX* p, int rows, int pages, cudaStream_t stream);
+GB_API int gb_attention_algo_x(const AttnParamsX* p, int dtype);
+
+// an AttnParams as the kernels take it: the later options off
+static inline AttnParamsX gb_attn_widen(const AttnParams& a) {
+    AttnParamsX x;
+    static_cast<AttnParams&>(x) = a;
+    x.dv = x.keep_first = x.sink = 0;
+    return x;
+}
 
 // matrix-state mixers
 GB_API int gb_gla_decay(float* z, const float* bias, int rows, int width, float tau, cudaStream_t stream);

@@ -40,7 +40,7 @@ __device__ __forceinline__ void load_page(bf16* dst, const bf16* src, int tid, i
 
 // ------------------------------------------------------------------------------------------
 template <int HD, bool QREG>
-__global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParams p) {
+__global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParamsX p) {
     constexpr int SD = HD + 8, KS = HD / 16, NF = HD / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
@@ -307,7 +307,7 @@ __device__ __forceinline__ void norm_rope_row(bf16* x, float* y, const float* __
 }
 
 template <int HD, bool QREG>
-__global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, RopeFuse f) {
+__global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParamsX p, RopeFuse f) {
     constexpr int SD = HD + 8, KS = HD / 16, NF = HD / 8;
     constexpr int STAGE = 2 * 64 * SD;  // elements: keys then values
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -580,7 +580,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParams p, Rope
 }
 
 template <int HD>
-int launch_prefill(const AttnParams& p, cudaStream_t stream) {
+int launch_prefill(const AttnParamsX& p, cudaStream_t stream) {
     constexpr bool QREG = HD <= 128;
     constexpr int SD = HD + 8;
     const int smem = 5 * 64 * SD * 2;
@@ -598,7 +598,7 @@ int launch_prefill(const AttnParams& p, cudaStream_t stream) {
 }
 
 template <int HD>
-int launch_decode(const AttnParams& p, const RopeFuse& f, cudaStream_t stream) {
+int launch_decode(const AttnParamsX& p, const RopeFuse& f, cudaStream_t stream) {
     constexpr bool QREG = HD <= 128;
     constexpr int SD = HD + 8;
     int smem = (16 * SD + DSTAGES * 2 * 64 * SD) * 2 + 4 * HD * 4 + 2 * HD * 2;
@@ -630,7 +630,7 @@ int launch_decode(const AttnParams& p, const RopeFuse& f, cudaStream_t stream) {
     return 0;
 }
 
-int check(const AttnParams& p, const char* who) {
+int check(const AttnParamsX& p, const char* who) {
     if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("%s: %d heads over %d kv heads", who, p.heads, p.kv_heads);
     if (p.d % 16 || p.d < 16 || (p.d > 128 && p.d != 256))
         GB_REFUSE("%s: head_dim %d is not one of 16, 32, ..., 128, 256 (other sizes up to 256 run on the CUDA-core kernel)", who, p.d);
@@ -658,7 +658,12 @@ int check(const AttnParams& p, const char* who) {
     }
 
 GB_API int gb_attention_prefill_mma(const AttnParams* pp, cudaStream_t stream) {
-    AttnParams p = *pp;
+    const AttnParamsX x = gb_attn_widen(*pp);
+    return gb_attention_prefill_mma_x(&x, stream);
+}
+
+GB_API int gb_attention_prefill_mma_x(const AttnParamsX* pp, cudaStream_t stream) {
+    AttnParamsX p = *pp;
     if (p.nseq <= 0 || p.max_q_len <= 0) return 0;
     if (int rc = check(p, "attention_prefill_mma")) return rc;
     if (p.num_splits != 1) GB_REFUSE("attention_prefill_mma: key splits are for single-token rows");
@@ -667,7 +672,12 @@ GB_API int gb_attention_prefill_mma(const AttnParams* pp, cudaStream_t stream) {
 }
 
 GB_API int gb_attention_decode_mma(const AttnParams* pp, cudaStream_t stream) {
-    AttnParams p = *pp;
+    const AttnParamsX x = gb_attn_widen(*pp);
+    return gb_attention_decode_mma_x(&x, stream);
+}
+
+GB_API int gb_attention_decode_mma_x(const AttnParamsX* pp, cudaStream_t stream) {
+    AttnParamsX p = *pp;
     if (p.nseq <= 0) return 0;
     if (int rc = check(p, "attention_decode_mma")) return rc;
     if (p.max_q_len != 1) GB_REFUSE("attention_decode_mma: rows of up to %d tokens; this kernel takes single tokens", p.max_q_len);
@@ -690,7 +700,7 @@ GB_API int gb_attention_decode_rope_accepts(int dtype, int d, int rot, int max_q
 // sequence's last page takes the token's own key and value from the row, and one CTA per kv head
 // stores them in the cache.  The same bits as the two kernels one after the other.
 GB_API int gb_attention_decode_mma_rope(const AttnParams* pp, const QkRopeParams* rp, cudaStream_t stream) {
-    AttnParams p = *pp;
+    AttnParamsX p = gb_attn_widen(*pp);
     const QkRopeParams& r = *rp;
     if (p.nseq <= 0) return 0;
     const char* who = "attention_decode_mma_rope";
@@ -704,7 +714,6 @@ GB_API int gb_attention_decode_mma_rope(const AttnParams* pp, const QkRopeParams
     if (r.write_kv && (r.k_plane != p.k_plane || r.v_plane != p.v_plane)) GB_REFUSE("%s: keys would be written to another plane than is read", who);
     if (!gb_attention_decode_rope_accepts(GB_BF16, p.d, r.rot, p.max_q_len)) GB_REFUSE("%s: head_dim %d, rotary width %d", who, p.d, r.rot);
     if (r.rot > 0 && (!r.cos_t || !r.sin_t)) GB_REFUSE("%s: rotary width %d without an angle table", who, r.rot);
-    if (r.q_b || r.k_b || r.v_b || r.pairs || (r.dv && r.dv != r.d)) GB_REFUSE("%s: biases, rotation by pairs and values of another size are the row-wise kernel's", who);
     RopeFuse f = {};
     f.on = 1;
     f.q_w = r.q_w;

@@ -21,7 +21,7 @@ constexpr int ROWS = 16;    // rows per CTA (4 warps)
 constexpr int KT = 32;      // keys per tile
 
 template <typename T, int NE>
-__global__ void __launch_bounds__(128) attn_simt_kernel(AttnParams p) {
+__global__ void __launch_bounds__(128) attn_simt_kernel(AttnParamsX p) {
     extern __shared__ float sm[];
     const int d = p.d, ks = d + 1;
     const int dv = p.dv > 0 ? p.dv : p.d, vs = dv + 1;   // values may be narrower or wider than keys
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
 }
 
 template <typename T, int NE>
-int launch_ne(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+int launch_ne(const AttnParamsX& p, dim3 grid, size_t smem, cudaStream_t stream) {
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(attn_simt_kernel<T, NE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -256,7 +256,7 @@ int launch_ne(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t stream) 
 }
 
 template <typename T>
-int launch(const AttnParams& p, cudaStream_t stream) {
+int launch(const AttnParamsX& p, cudaStream_t stream) {
     const int G = p.heads / p.kv_heads;
     const int GC = G < ROWS ? G : ROWS;
     const int hchunks = (G + GC - 1) / GC;
@@ -304,7 +304,12 @@ int gb_attention_merge_launch(const float* scratch, void* out, int dtype, int64_
 }
 
 GB_API int gb_attention_simt(const AttnParams* pp, int dtype, cudaStream_t stream) {
-    AttnParams p = *pp;
+    const AttnParamsX x = gb_attn_widen(*pp);
+    return gb_attention_simt_x(&x, dtype, stream);
+}
+
+GB_API int gb_attention_simt_x(const AttnParamsX* pp, int dtype, cudaStream_t stream) {
+    AttnParamsX p = *pp;
     if (p.nseq <= 0 || p.max_q_len <= 0) return 0;
     if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("attention: %d heads over %d kv heads", p.heads, p.kv_heads);
     if (p.d <= 0 || p.d > 256) GB_REFUSE("attention_simt: head_dim %d is outside [1, 256]", p.d);

@@ -157,7 +157,7 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 
 __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                    const __grid_constant__ CUtensorMap map_k,
-                                                                   const __grid_constant__ CUtensorMap map_v, AttnParams p,
+                                                                   const __grid_constant__ CUtensorMap map_v, AttnParamsX p,
                                                                    int by_kv_head) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -557,7 +557,12 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int cols, int64_t
 
 // rows: packed query rows in the q buffer; pages: pages in each cache plane
 GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, cudaStream_t stream) {
-    AttnParams p = *pp;
+    const AttnParamsX x = gb_attn_widen(*pp);
+    return gb_attention_prefill_tc5_x(&x, rows, pages, stream);
+}
+
+GB_API int gb_attention_prefill_tc5_x(const AttnParamsX* pp, int rows, int pages, cudaStream_t stream) {
+    AttnParamsX p = *pp;
     if (p.nseq <= 0 || p.max_q_len <= 0) return 0;
     const char* who = "attention_prefill_tc5";
     if (p.d != HD) GB_REFUSE("%s: head_dim %d; this kernel takes 128", who, p.d);

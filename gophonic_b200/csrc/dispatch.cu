@@ -137,6 +137,11 @@ GB_API int gb_gemm_add_accepts(const void* A, int a_dtype, const void* W, int w_
 enum GbAttnAlgo : int { GB_ATTN_SIMT = 0, GB_ATTN_DECODE_MMA = 1, GB_ATTN_PREFILL_MMA = 2, GB_ATTN_PREFILL_TC5 = 3 };
 
 GB_API int gb_attention_algo(const AttnParams* p, int dtype) {
+    const AttnParamsX x = gb_attn_widen(*p);
+    return gb_attention_algo_x(&x, dtype);
+}
+
+GB_API int gb_attention_algo_x(const AttnParamsX* p, int dtype) {
     if (dtype != GB_BF16 || (p->d & 15) || !(p->d <= 128 || p->d == 256)) return GB_ATTN_SIMT;
     if (p->dv && p->dv != p->d) return GB_ATTN_SIMT;   // values of another size than keys: the CUDA-core kernel only
     if (p->max_q_len == 1) return GB_ATTN_DECODE_MMA;

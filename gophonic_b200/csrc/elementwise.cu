@@ -65,9 +65,20 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
     }
 }
 
+GB_API int gb_embed_gather_scaled(const void* table, int table_dtype, const int* ids, int rows, int hidden, int vocab,
+                                  float* out, float* stats, int64_t stats_stride, const float* next_w, void* xn_out, int64_t ldxn,
+                                  float scale, cudaStream_t stream);
+
+// the entry point as it has always been: no scale
 GB_API int gb_embed_gather(const void* table, int table_dtype, const int* ids, int rows, int hidden, int vocab,
                            float* out, float* stats, int64_t stats_stride, const float* next_w, void* xn_out, int64_t ldxn,
-                           float scale, cudaStream_t stream) {
+                           cudaStream_t stream) {
+    return gb_embed_gather_scaled(table, table_dtype, ids, rows, hidden, vocab, out, stats, stats_stride, next_w, xn_out, ldxn, 1.0f, stream);
+}
+
+GB_API int gb_embed_gather_scaled(const void* table, int table_dtype, const int* ids, int rows, int hidden, int vocab,
+                                  float* out, float* stats, int64_t stats_stride, const float* next_w, void* xn_out, int64_t ldxn,
+                                  float scale, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) GB_REFUSE("embed_gather: hidden %d, vocab %d", hidden, vocab);
     if (next_w && (!xn_out || ldxn < hidden)) GB_REFUSE("embed_gather: a norm weight is given without room for its %d-wide rows", hidden);
@@ -335,7 +346,7 @@ GB_API int gb_swiglu(const void* gu, void* out, int dtype, int rows, int inter, 
 // float64 on the host and rounded to fp32 (internal/qwen3lm/evaluator.go:847-858).
 
 template <typename T>
-__global__ void qk_rope_kernel(QkRopeParams p) {
+__global__ void qk_rope_kernel(QkRopeParamsX p) {
     extern __shared__ float sh[];  // [4 warps][d]
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int r = blockIdx.x;
@@ -599,7 +610,15 @@ __global__ void __launch_bounds__(256) qk_rope_bf16_d128_wide_kernel(QkRopeParam
 }
 
 GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStream_t stream) {
-    QkRopeParams p = *pp;
+    QkRopeParamsX x;
+    static_cast<QkRopeParams&>(x) = *pp;
+    x.q_b = x.k_b = x.v_b = nullptr;
+    x.pairs = x.dv = 0;
+    return gb_qk_norm_rope_kv_write_x(&x, dtype, stream);
+}
+
+GB_API int gb_qk_norm_rope_kv_write_x(const QkRopeParamsX* pp, int dtype, cudaStream_t stream) {
+    QkRopeParamsX p = *pp;
     if (p.rows <= 0) return 0;
     if (p.d <= 0 || p.d > 1024) GB_REFUSE("qk_norm_rope: head_dim %d is outside [1, 1024]", p.d);
     if (p.rot < 0 || p.rot > p.d || (p.rot & 1)) GB_REFUSE("qk_norm_rope: rotary width %d must be even and <= head_dim %d", p.rot, p.d);

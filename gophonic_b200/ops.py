@@ -107,7 +107,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, stat
             raise KernelError(f"embed_gather: statistics for {stats.shape[0]} rows, {rows} rows")
         stride = stats.stride(0)
     ldxn = _check_next(next_weight, next_x, rows, hidden, "embed_gather")
-    _check(_lib.gb_embed_gather(_ptr(table), _code(table.dtype), _ptr(ids), c_int(rows), c_int(hidden),
+    _check(_lib.gb_embed_gather_scaled(_ptr(table), _code(table.dtype), _ptr(ids), c_int(rows), c_int(hidden),
                                 c_int(table.shape[0]), _ptr(out), _ptr(stats), c_int64(stride), _ptr(next_weight), _ptr(next_x),
                                 c_int64(ldxn), c_float(scale), _stream()))
 
@@ -562,7 +562,7 @@ def qk_norm_rope_kv_write(qkv: torch.Tensor, *args, **kwargs) -> None:
     rotary_dim, row_pos, row_seq, seq_slot, block_table, k_plane, v_plane, write_kv) and the keywords
     of ``_rope_params``."""
     p = _rope_params(qkv, *args, **kwargs)
-    _check(_lib.gb_qk_norm_rope_kv_write(byref(p), _code(qkv.dtype), _stream()))
+    _check(_lib.gb_qk_norm_rope_kv_write_x(byref(p), _code(qkv.dtype), _stream()))
 
 
 class _AttnParams(Structure):
@@ -631,16 +631,16 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
     p = _attn_params(q, out, k_plane, v_plane, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len, nseq, max_q_len,
                      heads, kv_heads, head_dim, scale, window, num_splits, scratch, value_dim, keep_first, sink)
     if algo == "auto":   # the library's own rule (head size, rows per sequence, alignment)
-        algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5")[int(_lib.gb_attention_algo(byref(p), _code(q.dtype)))]
+        algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5")[int(_lib.gb_attention_algo_x(byref(p), _code(q.dtype)))]
     nk = 2 if num_splits > 1 else 1
     if algo == "simt":
-        _check(_lib.gb_attention_simt(byref(p), _code(q.dtype), _stream()), nk)
+        _check(_lib.gb_attention_simt_x(byref(p), _code(q.dtype), _stream()), nk)
     elif algo == "decode_mma":
-        _check(_lib.gb_attention_decode_mma(byref(p), _stream()), nk)
+        _check(_lib.gb_attention_decode_mma_x(byref(p), _stream()), nk)
     elif algo == "prefill_mma":
-        _check(_lib.gb_attention_prefill_mma(byref(p), _stream()))
+        _check(_lib.gb_attention_prefill_mma_x(byref(p), _stream()))
     elif algo == "prefill_tc5":
-        _check(_lib.gb_attention_prefill_tc5(byref(p), c_int(q.shape[0]), c_int(k_plane.shape[0]), _stream()))
+        _check(_lib.gb_attention_prefill_tc5_x(byref(p), c_int(q.shape[0]), c_int(k_plane.shape[0]), _stream()))
     else:
         raise KernelError(f"attention: unknown algorithm '{algo}'")
     return algo

@@ -668,52 +668,6 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(HeadGateParams p) {
     T* y = (T*)p.y + r * p.y_stride + (int64_t)h * n;
     const float div = p.divisor ? p.divisor[(r * p.heads + h) * p.divisor_stride] : 1.f;
     const float* w = p.weight ? p.weight + (p.weight_per_head ? (int64_t)h * n : 0) : nullptr;
-    // heads of 128, 256, 384 or 512 whose rows are aligned: a lane takes four neighbouring elements of each
-    // 128 as one load (16 bytes of float32, 8 of bfloat16)
-    if (!(n & 127) && n <= 512 && !((uintptr_t)x & (4 * sizeof(TI) - 1)) && !((uintptr_t)g & (4 * sizeof(T) - 1)) &&
-        !((uintptr_t)y & (4 * sizeof(T) - 1)) && (!w || !((uintptr_t)w & 15))) {
-        float v[16], z[16], ww[16];
-        const int nv = n >> 7;
-        float ss = 0.f;
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            if (e < nv) {
-                const int i = 128 * e + 4 * lane;
-                load4<TI>(x + i, v + 4 * e);
-                load4<T>(g + i, z + 4 * e);
-                if (w) {
-                    const float4 w4 = *reinterpret_cast<const float4*>(w + i);
-                    ww[4 * e] = w4.x, ww[4 * e + 1] = w4.y, ww[4 * e + 2] = w4.z, ww[4 * e + 3] = w4.w;
-                }
-            }
-        }
-#pragma unroll
-        for (int e = 0; e < 16; e++) {
-            if ((e >> 2) < nv) {
-                if (p.divisor) v[e] /= div;
-                ss += v[e] * v[e];
-            }
-        }
-        float inv = 1.f;
-        if (p.normed) inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + p.eps);
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            if (e < nv) {
-                float o[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    float t = v[4 * e + u];
-                    if (p.normed) t *= inv;
-                    if (w) t *= ww[4 * e + u];
-                    const float zz = z[4 * e + u];
-                    const float sg = 1.f / (1.f + expf(-zz));
-                    o[u] = t * (p.gate_kind == 1 ? zz * sg : sg);
-                }
-                store4<T>(y + 128 * e + 4 * lane, o);
-            }
-        }
-        return;
-    }
     // heads of up to 256: every lane keeps its elements in registers, so x is read once and all of a
     // lane's loads (x, gate, weight) are in flight together
     if (n <= 256) {
@@ -768,8 +722,98 @@ __global__ void __launch_bounds__(128) head_norm_gate_kernel(HeadGateParams p) {
     }
 }
 
+// The same for heads of 128, 256, 384 or 512 whose rows are aligned.  A warp takes a span of up to 512
+// neighbouring elements of a row, which is 4, 2 or 1 whole heads (HB); a lane takes four neighbouring
+// elements of each 128 as one load (16 bytes of float32, 8 of bfloat16), all of them issued before
+// anything is computed: a head of 128 alone is too few bytes in flight a warp to keep the memory busy.
+template <typename TI, typename T>
+__global__ void __launch_bounds__(128) head_norm_gate_span_kernel(HeadGateParams p, int hb) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t r = blockIdx.x;
+    const int h0 = (blockIdx.y * 4 + warp) * hb;
+    if (h0 >= p.heads) return;
+    const int n = p.size, nv = n >> 7;                 // 128-element chunks a head
+    const int heads_here = p.heads - h0 < hb ? p.heads - h0 : hb;
+    const int chunks = heads_here * nv;                // <= 4
+    const TI* x = (const TI*)p.x + r * p.x_stride + (int64_t)h0 * n;
+    const T* g = (const T*)p.gate + r * p.gate_stride + (int64_t)h0 * n;
+    T* y = (T*)p.y + r * p.y_stride + (int64_t)h0 * n;
+    float v[16], z[16], ww[16], dv4[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        dv4[e] = 1.f;
+        if (e < chunks) {
+            const int i = 128 * e + 4 * lane;
+            load4<TI>(x + i, v + 4 * e);
+            load4<T>(g + i, z + 4 * e);
+            if (p.weight) {
+                const float* w = p.weight + (p.weight_per_head ? (int64_t)h0 * n + i : i % n);
+                const float4 w4 = *reinterpret_cast<const float4*>(w);
+                ww[4 * e] = w4.x, ww[4 * e + 1] = w4.y, ww[4 * e + 2] = w4.z, ww[4 * e + 3] = w4.w;
+            }
+            if (p.divisor) dv4[e] = p.divisor[(r * p.heads + h0 + e / nv) * p.divisor_stride];
+        }
+    }
+    float ss[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        ss[e] = 0.f;
+        if (e < chunks) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (p.divisor) v[4 * e + u] /= dv4[e];
+                ss[e] += v[4 * e + u] * v[4 * e + u];
+            }
+        }
+    }
+    float inv[4] = {1.f, 1.f, 1.f, 1.f};
+    if (p.normed) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) ss[e] = warp_sum(ss[e]);
+        // a head's sum of squares: its chunks' sums, in order
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            if (e < chunks) {
+                const int first = (e / nv) * nv;
+                float t = 0.f;
+#pragma unroll
+                for (int f = 0; f < 4; f++)
+                    if (f >= first && f < first + nv) t += ss[f];
+                inv[e] = 1.0f / sqrtf(t / (float)n + p.eps);
+            }
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        if (e < chunks) {
+            float o[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float t = v[4 * e + u];
+                if (p.normed) t *= inv[e];
+                if (p.weight) t *= ww[4 * e + u];
+                const float zz = z[4 * e + u];
+                const float sg = 1.f / (1.f + expf(-zz));
+                o[u] = t * (p.gate_kind == 1 ? zz * sg : sg);
+            }
+            store4<T>(y + 128 * e + 4 * lane, o);
+        }
+    }
+}
+
 template <typename TI, typename T>
 int launch_gate(const HeadGateParams& p, cudaStream_t stream) {
+    const int n = p.size;
+    const bool aligned = !((uintptr_t)p.x & (4 * sizeof(TI) - 1)) && !(p.x_stride & 3) && !((uintptr_t)p.gate & (4 * sizeof(T) - 1)) &&
+                         !(p.gate_stride & 3) && !((uintptr_t)p.y & (4 * sizeof(T) - 1)) && !(p.y_stride & 3) && !((uintptr_t)p.weight & 15);
+    if (!(n & 127) && n <= 512 && aligned) {
+        const int hb = 512 / n;     // whole heads in a span of 512 elements
+        dim3 grid(p.rows, (p.heads + 4 * hb - 1) / (4 * hb));
+        if (grid.y > 65535) GB_REFUSE("head_norm_gate: %d heads exceed one launch", p.heads);
+        head_norm_gate_span_kernel<TI, T><<<grid, 128, 0, stream>>>(p, hb);
+        GB_CHECK_LAUNCH("head_norm_gate");
+        return 0;
+    }
     dim3 grid(p.rows, (p.heads + 3) / 4);
     if (grid.y > 65535) GB_REFUSE("head_norm_gate: %d heads exceed one launch", p.heads);
     head_norm_gate_kernel<TI, T><<<grid, 128, 0, stream>>>(p);

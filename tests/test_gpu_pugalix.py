@@ -351,7 +351,7 @@ def test_head_norm_gate_and_decay_kernels(size):
     ops.use_device(0)
     dev = torch.device("cuda:0")
     rng = np.random.default_rng(0)
-    rows, heads = 7, 3
+    rows, heads = 7, (5 if size == 128 else 3)     # five heads of 128: a warp with four heads and one with one
     x = rng.standard_normal((rows, heads * size))
     g = rng.standard_normal((rows, heads * size))
     div = 0.5 + rng.random((rows, heads, 4))

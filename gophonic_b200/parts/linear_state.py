@@ -19,7 +19,6 @@ from .base import Mixer, Runtime, StateRequest, TensorDecl
 
 class _StateMixer(Mixer):
     capturable = True
-    extra_state = 0          # floats a head keeps beside its key_dim x value_dim matrix
 
     @classmethod
     def _per_head(cls, spec) -> int:

@@ -36,7 +36,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.base import KVRequest, StateRequest
+from ..parts.base import KVRequest, KVStateRequest, StateRequest
 
 PAGE = 64
 
@@ -105,6 +105,7 @@ class KVView:
     block_table: torch.Tensor  # [max_slots, max_pages_per_seq] int32
     writable: bool
     window: int
+    state: Optional[torch.Tensor] = None   # [max_slots, *shape]: fixed-size state beside the keys, if the run asked for it
 
 
 @dataclass
@@ -150,11 +151,18 @@ class Cache:
         self._kv_groups: Dict[Tuple[int, ...], List[int]] = {}
         self._state_groups: Dict[Tuple[Tuple[int, ...], torch.dtype], List[int]] = {}
         self._plane: Dict[int, Tuple[str, object, int]] = {}
+        self._beside: Dict[int, Tuple[object, int]] = {}     # the state plane of a run that asked for keys and state
         self._cache_of: Dict[int, Optional[int]] = {}
         for pos, (req, cache_of) in enumerate(requests):
             self._cache_of[pos] = cache_of
             if cache_of is not None or req is None:
                 continue
+            if isinstance(req, KVStateRequest):
+                key = (tuple(req.state.shape), req.state.dtype)
+                planes = self._state_groups.setdefault(key, [])
+                self._beside[pos] = (key, len(planes))
+                planes.append(pos)
+                req = req.kv
             if isinstance(req, KVRequest):
                 # values as wide as keys: the key every such group has always had; else the width is part of it
                 key = (req.kv_heads, req.head_dim, req.window)
@@ -214,7 +222,11 @@ class Cache:
             return None
         kind, key, ordinal = self._plane[at]
         if kind == "kv":
-            return KVView(self._k[key][ordinal], self._v[key][ordinal], self.block_table, writable, key[2])
+            state = None
+            if at in self._beside:
+                skey, sord = self._beside[at]
+                state = self._state[skey][sord]
+            return KVView(self._k[key][ordinal], self._v[key][ordinal], self.block_table, writable, key[2], state)
         return StateView(self._state[key][ordinal], writable)
 
     # ---- slots -------------------------------------------------------------------------

@@ -1,9 +1,11 @@
-from .spec import (AttentionSpec, DecayStateSpec, EmbeddingSpec, GatedAttentionSpec, HeadSpec, LayerSpec,
-                   MatrixMemorySpec, ModelSpec, NoPositionSpec, PairRotarySpec, RMSNormSpec, RotarySpec,
-                   ScheduleEntry, SwiGLUSpec, default_schedule)
+from .spec import (AttentionSpec, DecayStateSpec, DeltaRuleSpec, EmbeddingSpec, GatedAttentionSpec, HeadSpec, HyperLayerSpec,
+                   LayerSpec, MatrixMemorySpec, MoESpec, ModelSpec, NoPositionSpec, PairRotarySpec, RMSNormSpec, RotarySpec,
+                   ScheduleEntry, SigmoidAttentionSpec, SwiGLUSpec, default_schedule)
 from .qwen3 import ConfigError, Qwen3Config
 from .pugalix import PugalixConfig
+from .vepitar import VepitarConfig
 
-__all__ = ["AttentionSpec", "DecayStateSpec", "EmbeddingSpec", "GatedAttentionSpec", "HeadSpec", "LayerSpec",
-           "MatrixMemorySpec", "ModelSpec", "NoPositionSpec", "PairRotarySpec", "RMSNormSpec", "RotarySpec",
-           "ScheduleEntry", "SwiGLUSpec", "default_schedule", "ConfigError", "Qwen3Config", "PugalixConfig"]
+__all__ = ["AttentionSpec", "DecayStateSpec", "DeltaRuleSpec", "EmbeddingSpec", "GatedAttentionSpec", "HeadSpec", "HyperLayerSpec",
+           "LayerSpec", "MatrixMemorySpec", "MoESpec", "ModelSpec", "NoPositionSpec", "PairRotarySpec", "RMSNormSpec", "RotarySpec",
+           "ScheduleEntry", "SigmoidAttentionSpec", "SwiGLUSpec", "default_schedule", "ConfigError", "Qwen3Config", "PugalixConfig",
+           "VepitarConfig"]

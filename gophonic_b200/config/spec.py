@@ -19,12 +19,13 @@ from typing import Optional, Sequence, Tuple
 
 @dataclass(frozen=True)
 class RMSNormSpec:
-    """y = x * rsqrt(mean(x^2) + eps) * weight  (internal/qwen3lm/ops.go:251-254).  The weight is
-    the tensor ``prefix + tensor``."""
+    """y = x * rsqrt(mean(x^2) + eps) * (offset + weight)  (internal/qwen3lm/ops.go:251-254).  The
+    weight is the tensor ``prefix + tensor``; with ``offset`` 1 the checkpoint holds the weight's difference from one."""
     size: int
     eps: float
     kind: str = "rmsnorm"
     tensor: str = "weight"
+    offset: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -144,6 +145,72 @@ class MatrixMemorySpec:
 
 
 @dataclass(frozen=True)
+class DeltaRuleSpec:
+    """Generalized delta rule: per head a matrix state S (key_dim x value_dim, float32).  With the
+    receptance r, key k, value v, a decay w and a removal rate a per key channel and the unit key
+    u = k / sqrt(|k|^2 + key_eps):
+
+        S <- diag(w) S - (a * u) (u^T S) + k v^T   (both terms read the old S),   o = S^T r.
+
+    w = exp(-decay_scale * sigmoid(W2 tanh(W1 x) + w0)) with W1 of ``rank`` rows (None: the
+    checkpoint's), a = sigmoid(Wa x + b).  Each head's o is divided by its root mean square, the
+    heads together are multiplied by a weight and by sigmoid of a gate projection, and projected back."""
+    hidden: int
+    heads: int
+    key_dim: int
+    value_dim: int
+    rank: Optional[int]
+    decay_scale: float
+    key_eps: float
+    eps: float
+    kind: str = "delta_rule"
+
+
+@dataclass(frozen=True)
+class SigmoidAttentionSpec:
+    """Grouped-query attention whose weights are not normalised over the keys: a visible key j weighs
+    sigmoid((q_i . k_j) * scale + b_h), with b_h one number per head (``score_bias``).  Options:
+
+    * ``conv_taps`` > 0: a causal convolution over time on every channel of q, k and v directly after
+      the projection, y_t = sum_j c[:, j] u_(t - taps + 1 + j), zeros before the sequence's start; the
+      last taps - 1 projected rows of a sequence are part of its state;
+    * ``qk_norm``: q and k are divided by their root mean square per head; ``v_norm``: v likewise (the
+      cache holds the normed keys and values);
+    * ``window`` > 0: position i sees j with 0 <= i - j < window; 0: every j <= i;
+    * ``head_gate``: head h's output is multiplied by sigmoid of one number, row h of a further
+      projection of the mixer's input.
+
+    There is no position encoding."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    window: int = 0
+    conv_taps: int = 0
+    qk_norm: bool = True
+    v_norm: bool = True
+    score_bias: bool = True
+    head_gate: bool = True
+    eps: float = 1e-6
+    kind: str = "sigmoid_attention"
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """Mixture of experts: ``experts`` feed-forwards down(act(up(x))) without biases, act(z) = relu(z)^2,
+    of which a token uses ``top``.  Router scores s = softmax(Wr x) over all experts in float32; the
+    ``top`` largest are chosen and weigh their experts' outputs by s / (sum of the chosen s + renorm_eps)."""
+    hidden: int
+    experts: int
+    top: int
+    intermediate: int
+    renorm_eps: float = 1e-20
+    kind: str = "moe"
+
+
+@dataclass(frozen=True)
 class SwiGLUSpec:
     """down(silu(gate(x)) * up(x))  (internal/qwen3lm/ops.go:442-461).  ``names``: the tensors of the
     gate, up and down projections under the part's prefix."""
@@ -177,6 +244,30 @@ class LayerSpec:
     feed_forward_prefix: str = "mlp."
     mixer_norm_prefix: str = "input_layernorm."
     feed_forward_norm_prefix: str = "post_attention_layernorm."
+
+
+@dataclass(frozen=True)
+class HyperLayerSpec:
+    """One layer of the hyper-connection arrangement: the residual is ``streams`` copies x_1 .. x_s.  For
+    sublayer q (mixer, then feed-forward) with vectors in_q, out_q and a matrix mix_q ([from, to]):
+
+        u = sum_s in_q[s] x_s;   y = sublayer(norm_q(u));   x_t <- sum_s mix_q[s, t] x_s + mult * out_q[t] * y
+
+    for all t at once from the old streams.  ``streams`` 0 is the plain residual x <- x + mult * y: one
+    stream and no tensors.  The tensors of sublayer q are ``prefix + connection_prefixes[q] + "in" | "out" | "mix"``."""
+    prefix: str
+    mixer: object
+    feed_forward: object
+    mixer_norm: object
+    feed_forward_norm: object
+    streams: int = 0
+    residual_mult: float = 1.0
+    block: str = "hyper"
+    mixer_prefix: str = "mix."
+    feed_forward_prefix: str = "mlp."
+    mixer_norm_prefix: str = "norm1"
+    feed_forward_norm_prefix: str = "norm2"
+    connection_prefixes: Tuple[str, str] = ("hc1.", "hc2.")
 
 
 @dataclass(frozen=True)
@@ -223,6 +314,7 @@ class ModelSpec:
     final_norm: object
     final_norm_name: str
     head: HeadSpec
+    streams: int = 1      # copies of the residual the blocks keep (hyper-connections); the final norm reads their sum
 
     def validate(self) -> None:
         if not self.layers:

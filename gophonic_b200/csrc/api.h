@@ -175,3 +175,111 @@ static inline AttnParamsX gb_attn_widen(const AttnParams& a) {
 GB_API int gb_gla_decay(float* z, const float* bias, int rows, int width, float tau, cudaStream_t stream);
 GB_API int gb_state_scan(const LinearStateParams* p, int dtype, cudaStream_t stream);
 GB_API int gb_head_norm_gate(const HeadGateParams* p, int x_dtype, int dtype, cudaStream_t stream);
+
+// Hyper-connections: S streams of the residual, mixed by a sublayer's output and read for the next norm.
+struct HyperParams {
+    float* streams;          // stream s, row r: streams + s * stream_stride + r * width
+    int64_t stream_stride;
+    int n_streams, rows, width;
+    const float* y;          // [rows, width] the sublayer's output, or null: the streams are only read
+    const float* mix;        // [S, S] indexed [from, to], or null: the identity
+    const float* out_coef;   // [S] or null: ones
+    float mult;              // on the sublayer's output
+    const float* in_coef;    // [S] or null: ones (the plain sum of the streams)
+    const float* norm_w;     // [width]: the weight the normed sum is multiplied by
+    float eps;
+    void* x_out;             // [rows, width] in the activation dtype, or null: nothing is normed
+    const int* row_index;    // rows to read (x_out row i from streams row row_index[i]), or null
+};
+GB_API int gb_hyper_mix_norm(const HyperParams* p, int out_dtype, cudaStream_t stream);
+
+// The generalized delta rule: S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r per (sequence, head).
+struct DeltaStateParams {
+    const void* rkv;        // rows of the fused projection (activation dtype): r, k and v heads at the offsets below
+    int64_t row_stride;
+    int r_off, k_off, v_off;
+    float* decay;           // [rows, decay_stride]: heads x d pre-activations of the decay; the decays afterwards
+    int64_t decay_stride;
+    const float* decay_bias;   // [heads * d] or null
+    float decay_scale;         // w = exp(-decay_scale * sigmoid(z))
+    float* remove;          // [rows, remove_stride]: heads x d pre-activations of the removal rate; a * u afterwards
+    int64_t remove_stride;
+    const float* remove_bias;
+    float* unit;            // [rows, unit_stride]: heads x d, receives the unit keys
+    int64_t unit_stride;
+    float key_eps;          // under the root of the key's length
+    float* dots;            // [rows, heads, 2]: receives (a u) . r and k . r
+    float* state;           // [slots, ...]: per head d x dv
+    int64_t slot_stride, head_stride;
+    float* out;             // [rows, out_stride]: heads x dv sums S^T r
+    int64_t out_stride;
+    const int* seq_slot;
+    const int* seq_q_start;
+    const int* seq_q_len;
+    int rows, nseq, heads, d, dv;
+    int max_slots;
+    int max_q_len;          // most rows a sequence brings; 1 selects the kernel for single tokens
+};
+GB_API int gb_delta_scan(const DeltaStateParams* p, int dtype, cudaStream_t stream);
+GB_API int gb_tanh(float* z, int64_t n, cudaStream_t stream);
+
+// Short causal convolution over time on the projected q | k | v, head norms, q out and k, v into the cache.
+struct ConvQkvParams {
+    const void* qkv;        // [rows, row_stride]: q heads, k heads, v heads (then anything else)
+    int64_t row_stride;
+    const float* conv_w;    // [channels, taps] or null with taps 0
+    int taps, channels;
+    float* state;           // [slots, state_slot_stride]: the last taps - 1 projected rows, [taps - 1][channels]
+    int64_t state_slot_stride;
+    int qk_norm, v_norm;
+    float eps;
+    void* q_out;            // [rows, q_out_stride]
+    int64_t q_out_stride;
+    const int* row_pos;
+    const int* row_seq;
+    const int* seq_slot;
+    const int* seq_q_start;
+    const int* seq_q_len;
+    const int* block_table;
+    int bt_stride;
+    void* k_plane;
+    void* v_plane;
+    int rows, nseq, heads, kv_heads, d, dv;
+    int pages, max_slots;
+};
+GB_API int gb_conv_qkv(const ConvQkvParams* p, int dtype, cudaStream_t stream);
+
+// Attention with sigmoid weights: the softmax kernel's parameters, a bias per head on the score and a gate per head.
+struct SigmoidAttnParams : AttnParamsX {
+    const float* score_bias;   // [heads] or null
+    const void* gate;          // [rows, gate_stride] (activation dtype): heads pre-activations, or null
+    int64_t gate_stride;
+};
+GB_API int gb_attention_sigmoid(const SigmoidAttnParams* p, int dtype, cudaStream_t stream);
+
+// Mixture of experts.
+struct MoeRouteParams {
+    const float* logits;    // [rows, logits_stride]
+    int64_t logits_stride;
+    int rows, experts, top;
+    float renorm_eps;
+    float* dense;           // [rows, experts]: the weight of every expert, 0 where not chosen
+    int* index;             // [rows, top]
+    float* weight;          // [rows, top]
+};
+GB_API int gb_moe_route(const MoeRouteParams* p, cudaStream_t stream);
+GB_API int gb_moe_act(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
+                      int dtype, cudaStream_t stream);
+struct MoeRowsParams {
+    const void* x;          // [rows, x_stride] activation dtype
+    int64_t x_stride;
+    const void* up;         // [experts * ff, hidden]: the up matrices one above the other
+    const void* down;       // [hidden, experts * ff]: the down matrices side by side
+    void* act;              // [rows, top, ff] scratch, activation dtype
+    float* out;             // [rows, out_stride]
+    int64_t out_stride;
+    const int* index;
+    const float* weight;
+    int rows, experts, top, ff, hidden;
+};
+GB_API int gb_moe_rows(const MoeRowsParams* p, int dtype, int w_dtype, cudaStream_t stream);

@@ -48,6 +48,10 @@ SOURCES = [
     "attention_mma.cu",
     "attention_tc5.cu",
     "linear_state.cu",
+    "delta_state.cu",
+    "attention_sigmoid.cu",
+    "hyper.cu",
+    "moe.cu",
     "sampling.cu",
     "no_alloc.cu",
     "dispatch.cu",

@@ -1,0 +1,186 @@
+// Mixture of experts: the router's choice and the experts' activation.
+//
+// moe_route: per row, scores s = softmax(z) over all experts in fp32, the `top` largest chosen (of equal
+// scores the lower index first), weights s / (sum of the chosen s + renorm_eps).  The weights are left
+// twice: as a dense row [experts] with zeros for the experts not chosen, which is what the stacked
+// products of a step of many rows multiply by, and as `top` (index, weight) pairs for a step of few rows
+// that reads only the chosen experts' matrices.
+//
+// moe_act: act[r, e * ff + i] = weight[r, e] * relu(up[r, e * ff + i])^2: the activation of every expert's
+// hidden layer with the row's weight for that expert folded in, so that one product with the experts' down
+// matrices side by side gives the weighted sum of the chosen experts' outputs (an expert that was not
+// chosen contributes exact zeros).
+//
+// moe_up_rows / moe_down_rows: the same feed-forward for a step of few rows, reading only the chosen
+// experts' matrices (a warp a hidden unit, or an output column, of one (row, choice) pair).
+#include "api.h"
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+
+constexpr int MAX_EXPERTS_PER_LANE = 16;   // experts up to 512
+
+__global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 4 + warp;
+    if (row >= p.rows) return;
+    const int E = p.experts;
+    const float* z = p.logits + row * p.logits_stride;
+    float s[MAX_EXPERTS_PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < MAX_EXPERTS_PER_LANE; e++) {
+        const int i = lane + 32 * e;
+        s[e] = i < E ? z[i] : -INFINITY;
+        mx = fmaxf(mx, s[e]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int e = 0; e < MAX_EXPERTS_PER_LANE; e++) {
+        const int i = lane + 32 * e;
+        s[e] = i < E ? expf(s[e] - mx) : -1.f;     // scores are positive; -1 marks what is absent or taken
+        if (i < E) sum += s[e];
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    float* dense = p.dense + row * E;
+    for (int i = lane; i < E; i += 32) dense[i] = 0.f;
+    float chosen_sum = 0.f;
+    float my_w = 0.f;      // lane k keeps the k-th choice
+    int my_i = 0;
+    for (int k = 0; k < p.top; k++) {
+        float best = -1.f;
+        int best_i = 0x7fffffff;
+#pragma unroll
+        for (int e = 0; e < MAX_EXPERTS_PER_LANE; e++) {
+            const int i = lane + 32 * e;
+            if (s[e] > best) best = s[e], best_i = i;     // within a lane indices grow with e: the first of equals stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ob > best || (ob == best && oi < best_i)) best = ob, best_i = oi;
+        }
+#pragma unroll
+        for (int e = 0; e < MAX_EXPERTS_PER_LANE; e++)
+            if (lane + 32 * e == best_i) s[e] = -1.f;
+        const float sc = best * inv;
+        chosen_sum += sc;
+        if (lane == (k & 31)) my_w = sc, my_i = best_i;
+        if (k >= 32 && lane == 0) {}   // more than 32 choices are refused on the host
+    }
+    const float norm = 1.f / (chosen_sum + p.renorm_eps);
+    __syncwarp();
+    if (lane < p.top) {
+        const float w = my_w * norm;
+        dense[my_i] = w;
+        p.index[row * p.top + lane] = my_i;
+        p.weight[row * p.top + lane] = w;
+    }
+}
+
+template <typename T>
+__global__ void moe_act_kernel(const T* __restrict__ up, int64_t up_stride, const float* __restrict__ dense, T* __restrict__ act,
+                               int64_t act_stride, int rows, int experts, int ff) {
+    const int64_t n = (int64_t)experts * ff;
+    const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * n) return;
+    const int64_t r = idx / n, c = idx % n;
+    const float w = dense[r * experts + c / ff];
+    const float z = fmaxf(to_f32<T>(up[r * up_stride + c]), 0.f);
+    act[r * act_stride + c] = from_f32<T>(w * z * z);
+}
+
+// few rows: act[r, k, i] = weight[r, k] * relu(W_up[index[r, k]][i, :] . x[r])^2, a warp a hidden unit
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) moe_up_rows_kernel(MoeRowsParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i = blockIdx.x * 4 + warp;
+    const int pair = blockIdx.y;            // row * top + k
+    if (i >= p.ff) return;
+    const int r = pair / p.top;
+    const int e = p.index[pair];
+    const TW* w = (const TW*)p.up + ((int64_t)e * p.ff + i) * p.hidden;
+    const T* x = (const T*)p.x + (int64_t)r * p.x_stride;
+    float a = 0.f;
+    for (int c = lane; c < p.hidden; c += 32) a = fmaf(to_f32<TW>(w[c]), to_f32<T>(x[c]), a);
+    a = warp_sum(a);
+    if (lane == 0) {
+        // the same roundings as the stacked path: the product in the activation dtype, then the activation
+        const float z = fmaxf(to_f32<T>(from_f32<T>(a)), 0.f);
+        ((T*)p.act)[(int64_t)pair * p.ff + i] = from_f32<T>(p.weight[pair] * z * z);
+    }
+}
+
+// out[r, c] = sum_k W_down[index[r, k]][c, :] . act[r, k, :], a warp an output column of a row
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) moe_down_rows_kernel(MoeRowsParams p) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 4 + warp;
+    const int r = blockIdx.y;
+    if (c >= p.hidden) return;
+    float a = 0.f;
+    for (int k = 0; k < p.top; k++) {
+        const int pair = r * p.top + k;
+        const int e = p.index[pair];
+        const TW* w = (const TW*)p.down + ((int64_t)c * p.experts + e) * p.ff;      // the down matrices side by side: [hidden, experts * ff]
+        const T* z = (const T*)p.act + (int64_t)pair * p.ff;
+        for (int i = lane; i < p.ff; i += 32) a = fmaf(to_f32<TW>(w[i]), to_f32<T>(z[i]), a);
+    }
+    a = warp_sum(a);
+    if (lane == 0) p.out[(int64_t)r * p.out_stride + c] = a;
+}
+
+}  // namespace
+
+GB_API int gb_moe_route(const MoeRouteParams* pp, cudaStream_t stream) {
+    MoeRouteParams p = *pp;
+    if (p.rows <= 0) return 0;
+    if (p.experts <= 0 || p.experts > 32 * MAX_EXPERTS_PER_LANE) GB_REFUSE("moe_route: %d experts; 1 to %d", p.experts, 32 * MAX_EXPERTS_PER_LANE);
+    if (p.top <= 0 || p.top > p.experts || p.top > 32) GB_REFUSE("moe_route: %d of %d experts a token; at most 32", p.top, p.experts);
+    if (!p.logits || !p.dense || !p.index || !p.weight) GB_REFUSE("moe_route: a tensor is missing");
+    moe_route_kernel<<<(p.rows + 3) / 4, 128, 0, stream>>>(p);
+    GB_CHECK_LAUNCH("moe_route");
+    return 0;
+}
+
+GB_API int gb_moe_act(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
+                      int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (experts <= 0 || ff <= 0) GB_REFUSE("moe_act: %d experts of %d", experts, ff);
+    const int64_t total = (int64_t)rows * experts * ff;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == GB_F32)
+        moe_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)up, up_stride, dense, (float*)act, act_stride, rows, experts, ff);
+    else if (dtype == GB_BF16)
+        moe_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)up, up_stride, dense, (__nv_bfloat16*)act, act_stride,
+                                                                  rows, experts, ff);
+    else
+        GB_REFUSE("moe_act: unknown dtype %d", dtype);
+    GB_CHECK_LAUNCH("moe_act");
+    return 0;
+}
+
+GB_API int gb_moe_rows(const MoeRowsParams* pp, int dtype, int w_dtype, cudaStream_t stream) {
+    MoeRowsParams p = *pp;
+    if (p.rows <= 0) return 0;
+    if (p.experts <= 0 || p.top <= 0 || p.ff <= 0 || p.hidden <= 0) GB_REFUSE("moe_rows: %d experts, %d a token, %d x %d", p.experts, p.top, p.ff, p.hidden);
+    if (!p.x || !p.up || !p.down || !p.act || !p.out || !p.index || !p.weight) GB_REFUSE("moe_rows: a tensor is missing");
+    dim3 ugrid((p.ff + 3) / 4, p.rows * p.top), dgrid((p.hidden + 3) / 4, p.rows);
+    if (ugrid.y > 65535) GB_REFUSE("moe_rows: %d rows exceed one launch", p.rows);
+    if (dtype == GB_BF16 && w_dtype == GB_BF16) {
+        moe_up_rows_kernel<__nv_bfloat16, __nv_bfloat16><<<ugrid, 128, 0, stream>>>(p);
+        moe_down_rows_kernel<__nv_bfloat16, __nv_bfloat16><<<dgrid, 128, 0, stream>>>(p);
+    } else if (dtype == GB_F32 && w_dtype == GB_F32) {
+        moe_up_rows_kernel<float, float><<<ugrid, 128, 0, stream>>>(p);
+        moe_down_rows_kernel<float, float><<<dgrid, 128, 0, stream>>>(p);
+    } else {
+        GB_REFUSE("moe_rows: activations of dtype %d with weights of dtype %d", dtype, w_dtype);
+    }
+    GB_CHECK_LAUNCH("moe_rows");
+    return 0;
+}

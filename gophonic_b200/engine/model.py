@@ -53,6 +53,11 @@ class Model:
         self.embedding = tensors[spec.embedding.name]
         self.blocks = [registry.part_class("block", layer.block)(layer, layer.prefix, tensors, runtime)
                        for layer in spec.layers]
+        # a block arrangement may keep the residual in several streams; then every block must
+        self._takes_streams = [bool(getattr(b, "takes_streams", False)) for b in self.blocks]
+        self.streams = int(getattr(spec, "streams", 1))
+        if any(self._takes_streams) != all(self._takes_streams) or (self.streams > 1 and not all(self._takes_streams)):
+            raise ValueError("model spec: a residual kept in streams needs blocks that take streams, all of them")
         # a block arrangement may take the norm that follows it (to prepare the residual's rows for it)
         self._takes_next_norm = ["next_norm" in inspect.signature(b.forward).parameters for b in self.blocks]
         norm_prefix = final_norm_prefix(spec)
@@ -136,6 +141,8 @@ class Model:
         [len(want_rows), vocab] for the wanted packed rows (None if none are wanted)."""
         ops = self.rt.ops
         rows = batch.rows
+        if self._takes_streams[0]:
+            return self._forward_streams(batch, cache, want_rows)
         h = torch.empty((rows, self.spec.hidden), dtype=torch.float32, device=self.rt.device)
         # What is still owed to the residual travels from block to block: an addend not yet added, the
         # rows' statistics (``RowStats``) where the last kernel left them, or nothing.
@@ -170,6 +177,28 @@ class Model:
         n = want_rows.numel()
         x = torch.empty((n, self.spec.hidden), dtype=self.rt.act_dtype, device=self.rt.device)
         self.final_norm.forward(h, x, delta, rows=want_rows)
+        logits = torch.empty((n, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
+        ops.gemm(x, self.head, logits)
+        return logits
+
+    def _forward_streams(self, batch, cache: Cache, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """The same pass for blocks that keep the residual in streams: all streams start as the embedding
+        output, what a block's last sublayer leaves is spread over them by whoever reads them next, and the
+        final norm reads their sum."""
+        ops = self.rt.ops
+        rows, S = batch.rows, self.streams
+        streams = torch.empty((S, rows, self.spec.hidden), dtype=torch.float32, device=self.rt.device)
+        scale = float(getattr(self.spec.embedding, "scale", 1.0))
+        for s in range(S):
+            ops.embed_gather(self.embedding, batch.ids, streams[s], scale=scale)
+        pending = None
+        for pos, entry in enumerate(self.spec.schedule):
+            pending = self.blocks[entry.layer].forward(batch, streams, pending, cache.view(pos))
+        if want_rows is None or want_rows.numel() == 0:
+            return None
+        n = want_rows.numel()
+        x = torch.empty((n, self.spec.hidden), dtype=self.rt.act_dtype, device=self.rt.device)
+        self.blocks[self.spec.schedule[-1].layer].finish(streams, pending, self.final_norm, x, want_rows)
         logits = torch.empty((n, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
         ops.gemm(x, self.head, logits)
         return logits

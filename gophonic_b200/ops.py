@@ -471,7 +471,7 @@ def checked_status():
     found out of bounds since the last call (the access was skipped or redirected, nothing faulted).
     Always None in the ordinary build, whose kernels carry no checks.  Synchronises."""
     out = (c_int * 4)()
-    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5", "linear_state"):
+    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5", "linear_state", "delta_state", "attention_sigmoid"):
         code = int(getattr(_lib, "gb_checked_status_" + name)(out))
         if code or out[3]:
             return name, _CHECK_NAMES.get(code, f"code {code}"), out[1], out[2], out[3]
@@ -934,3 +934,256 @@ def f32_to_bf16(a: torch.Tensor, out: torch.Tensor) -> None:
     if a.numel() != out.numel():
         raise KernelError("f32_to_bf16: sizes differ")
     _check(_lib.gb_f32_to_bf16(_ptr(a), _ptr(out), c_int64(a.numel()), _stream()))
+
+
+# ---- hyper-connections -----------------------------------------------------------------------
+class _HyperParams(Structure):
+    _fields_ = [
+        ("streams", c_void_p), ("stream_stride", c_int64), ("n_streams", c_int), ("rows", c_int), ("width", c_int),
+        ("y", c_void_p), ("mix", c_void_p), ("out_coef", c_void_p), ("mult", c_float), ("in_coef", c_void_p),
+        ("norm_w", c_void_p), ("eps", c_float), ("x_out", c_void_p), ("row_index", c_void_p),
+    ]
+
+
+def hyper_mix_norm(streams: torch.Tensor, y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                   out_coef: Optional[torch.Tensor] = None, mult: float = 1.0, in_coef: Optional[torch.Tensor] = None,
+                   norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, x_out: Optional[torch.Tensor] = None,
+                   rows: Optional[torch.Tensor] = None) -> None:
+    """The two row-wise steps around a sublayer of a residual kept in S streams (``streams`` float32
+    [S, rows, width]), either or both in one pass.  With ``y`` (float32 [rows, width], a sublayer's
+    output): streams[t] <- sum_s mix[s, t] streams[s] + mult * out_coef[t] * y for all t from the old
+    values (``mix`` None: the identity; ``out_coef`` None: ones).  With ``x_out`` (activation dtype):
+    u = sum_s in_coef[s] streams[s] (None: the plain sum) of the new values and
+    x_out = u / sqrt(mean(u^2) + eps) * norm_weight.  With ``rows`` (int32 indices) x_out[i] is made
+    from row rows[i] and the streams are left as they were."""
+    _need(streams, "streams", torch.float32, 3)
+    S, n, width = streams.shape
+    for t, nm, shape in ((mix, "mix", (S, S)), (out_coef, "out coefficients", (S,)), (in_coef, "in coefficients", (S,)),
+                         (norm_weight, "norm weight", (width,)), (y, "sublayer output", (n, width))):
+        if t is not None:
+            _need(t, nm, torch.float32)
+            if tuple(t.shape) != shape:
+                raise KernelError(f"hyper_mix_norm: {nm} {tuple(t.shape)}, want {shape}")
+    out_rows = n
+    if rows is not None:
+        _need(rows, "row index", torch.int32, 1)
+        out_rows = rows.numel()
+    if x_out is not None:
+        _need(x_out, "normed rows", dim=2)
+        if x_out.shape != (out_rows, width):
+            raise KernelError(f"hyper_mix_norm: normed rows {tuple(x_out.shape)}, want {(out_rows, width)}")
+    p = _HyperParams(streams.data_ptr(), streams.stride(0), S, out_rows, width, 0 if y is None else y.data_ptr(),
+                     0 if mix is None else mix.data_ptr(), 0 if out_coef is None else out_coef.data_ptr(), mult,
+                     0 if in_coef is None else in_coef.data_ptr(), 0 if norm_weight is None else norm_weight.data_ptr(), eps,
+                     0 if x_out is None else x_out.data_ptr(), 0 if rows is None else rows.data_ptr())
+    _check(_lib.gb_hyper_mix_norm(byref(p), _code(x_out.dtype) if x_out is not None else F32, _stream()))
+
+
+# ---- the generalized delta rule ---------------------------------------------------------------
+class _DeltaStateParams(Structure):
+    _fields_ = [
+        ("rkv", c_void_p), ("row_stride", c_int64), ("r_off", c_int), ("k_off", c_int), ("v_off", c_int),
+        ("decay", c_void_p), ("decay_stride", c_int64), ("decay_bias", c_void_p), ("decay_scale", c_float),
+        ("remove", c_void_p), ("remove_stride", c_int64), ("remove_bias", c_void_p),
+        ("unit", c_void_p), ("unit_stride", c_int64), ("key_eps", c_float), ("dots", c_void_p),
+        ("state", c_void_p), ("slot_stride", c_int64), ("head_stride", c_int64), ("out", c_void_p), ("out_stride", c_int64),
+        ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
+        ("rows", c_int), ("nseq", c_int), ("heads", c_int), ("d", c_int), ("dv", c_int), ("max_slots", c_int), ("max_q_len", c_int),
+    ]
+
+
+def delta_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, heads: int, d: int, dv: int, decay: torch.Tensor,
+               decay_bias: Optional[torch.Tensor], decay_scale: float, remove: torch.Tensor, remove_bias: Optional[torch.Tensor],
+               key_eps: float, state: torch.Tensor, out: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
+               seq_q_len: torch.Tensor, nseq: int, max_q_len: int = 0) -> None:
+    """The generalized delta rule over the rows of a step, token by token, for every (sequence, head):
+    S <- diag(w) S - (a u)(u^T S) + k v^T from the old S, o = S^T r, with u the key over its length
+    (``key_eps`` under the root).  ``decay`` and ``remove`` (float32 [rows, heads * d]) hold pre-activations and
+    are overwritten: w = exp(-decay_scale * sigmoid(decay + decay_bias)), a = sigmoid(remove + remove_bias).
+    ``state`` [slots, heads, d * dv] float32 is read and left updated, ``out`` [rows, heads * dv] float32
+    receives the sums.  ``max_q_len`` 1: every sequence brings one token, which has a kernel of its own."""
+    _need(rkv, "delta_scan rows", dim=2, contiguous=False)
+    _need(state, "state", torch.float32, 3)
+    _need(out, "delta_scan out", torch.float32, 2)
+    rows = rkv.shape[0]
+    if (rkv.stride(1) != 1 or out.shape != (rows, heads * dv) or state.shape[1] != heads or state.shape[2] < d * dv
+            or max(r_off, k_off) + heads * d > rkv.shape[1] or v_off + heads * dv > rkv.shape[1]):
+        raise KernelError(f"delta_scan: rows {tuple(rkv.shape)}, state {tuple(state.shape)}, out {tuple(out.shape)} for "
+                          f"{heads} heads of {d} x {dv}")
+    for t, nm in ((decay, "decay pre-activations"), (remove, "removal pre-activations")):
+        _need(t, nm, torch.float32, 2, contiguous=False)
+        if t.shape != (rows, heads * d) or t.stride(1) != 1:
+            raise KernelError(f"delta_scan: {nm} {tuple(t.shape)} for {heads} heads of {d}")
+    for t, nm in ((decay_bias, "decay bias"), (remove_bias, "removal bias")):
+        if t is not None:
+            _need(t, nm, torch.float32, 1)
+            if t.numel() != heads * d:
+                raise KernelError(f"delta_scan: {nm} of {t.numel()} for {heads} heads of {d}")
+    for t, nm in ((seq_slot, "seq_slot"), (seq_q_start, "seq_q_start"), (seq_q_len, "seq_q_len")):
+        _need(t, nm, torch.int32, 1)
+        if t.numel() < nseq:
+            raise KernelError(f"delta_scan: {nm} has {t.numel()} entries for {nseq} sequences")
+    unit = torch.empty((rows, heads * d), dtype=torch.float32, device=rkv.device)
+    dots = torch.empty((rows, heads, 2), dtype=torch.float32, device=rkv.device)
+    p = _DeltaStateParams(rkv.data_ptr(), rkv.stride(0), r_off, k_off, v_off, decay.data_ptr(), decay.stride(0),
+                          0 if decay_bias is None else decay_bias.data_ptr(), decay_scale, remove.data_ptr(), remove.stride(0),
+                          0 if remove_bias is None else remove_bias.data_ptr(), unit.data_ptr(), unit.stride(0), key_eps,
+                          dots.data_ptr(), state.data_ptr(), state.stride(0), state.stride(1), out.data_ptr(), out.stride(0),
+                          seq_slot.data_ptr(), seq_q_start.data_ptr(), seq_q_len.data_ptr(), rows, nseq, heads, d, dv,
+                          state.shape[0], int(max_q_len))
+    _check(_lib.gb_delta_scan(byref(p), _code(rkv.dtype), _stream()), 2)
+
+
+def tanh_(z: torch.Tensor) -> None:
+    """In place: z = tanh(z), float32."""
+    _need(z, "tanh rows", torch.float32)
+    _check(_lib.gb_tanh(_ptr(z), c_int64(z.numel()), _stream()))
+
+
+# ---- attention with sigmoid weights and a short convolution ahead of it -----------------------
+class _ConvQkvParams(Structure):
+    _fields_ = [
+        ("qkv", c_void_p), ("row_stride", c_int64), ("conv_w", c_void_p), ("taps", c_int), ("channels", c_int),
+        ("state", c_void_p), ("state_slot_stride", c_int64), ("qk_norm", c_int), ("v_norm", c_int), ("eps", c_float),
+        ("q_out", c_void_p), ("q_out_stride", c_int64), ("row_pos", c_void_p), ("row_seq", c_void_p), ("seq_slot", c_void_p),
+        ("seq_q_start", c_void_p), ("seq_q_len", c_void_p), ("block_table", c_void_p), ("bt_stride", c_int),
+        ("k_plane", c_void_p), ("v_plane", c_void_p), ("rows", c_int), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int),
+        ("d", c_int), ("dv", c_int), ("pages", c_int), ("max_slots", c_int),
+    ]
+
+
+def conv_qkv(qkv: torch.Tensor, q_out: torch.Tensor, heads: int, kv_heads: int, head_dim: int, value_dim: int,
+             conv_weight: Optional[torch.Tensor], state: Optional[torch.Tensor], qk_norm: bool, v_norm: bool, eps: float,
+             batch, block_table: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor) -> None:
+    """Per row of the projected q | k | v (``qkv``, whose rows may be wider): a causal convolution over time on
+    every channel (``conv_weight`` float32 [channels, taps]; None: none), reaching back into the step's earlier
+    rows of the same sequence and, before them, into ``state`` (float32 [slots, (taps - 1) * channels], the
+    sequence's last projected rows, left updated); each head over its root mean square (``qk_norm``,
+    ``v_norm``); q into ``q_out`` [rows, heads * head_dim], k and v into the cache at the row's position."""
+    _need(qkv, "qkv", dim=2, contiguous=False)
+    _need(q_out, "q out", qkv.dtype, 2, contiguous=False)
+    rows = qkv.shape[0]
+    channels = (heads + kv_heads) * head_dim + kv_heads * value_dim
+    if qkv.stride(1) != 1 or qkv.shape[1] < channels or q_out.shape != (rows, heads * head_dim) or q_out.stride(1) != 1:
+        raise KernelError(f"conv_qkv: qkv {tuple(qkv.shape)}, q out {tuple(q_out.shape)} for {heads}+{kv_heads} heads of {head_dim} / {value_dim}")
+    taps = 0
+    if conv_weight is not None:
+        _need(conv_weight, "convolution weights", torch.float32, 2)
+        taps = conv_weight.shape[1]
+        if conv_weight.shape[0] != channels:
+            raise KernelError(f"conv_qkv: convolution weights {tuple(conv_weight.shape)} for {channels} channels")
+    slot_stride = 0
+    if taps > 1:
+        if state is None:
+            raise KernelError("conv_qkv: a convolution needs the sequences' state")
+        _need(state, "convolution state", torch.float32, 2, contiguous=False)
+        if state.shape[1] < (taps - 1) * channels or state.stride(1) != 1:
+            raise KernelError(f"conv_qkv: state {tuple(state.shape)} for {taps - 1} rows of {channels}")
+        slot_stride = state.stride(0)
+    for t, nm, n in ((k_plane, "key plane", head_dim), (v_plane, "value plane", value_dim)):
+        _need(t, nm, qkv.dtype, 4)
+        if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != n:
+            raise KernelError(f"conv_qkv: {nm} {tuple(t.shape)} for {kv_heads} kv heads of {n}")
+    _need(block_table, "block table", torch.int32, 2)
+    p = _ConvQkvParams(qkv.data_ptr(), qkv.stride(0), 0 if conv_weight is None else conv_weight.data_ptr(), taps, channels,
+                       0 if state is None or taps <= 1 else state.data_ptr(), slot_stride, 1 if qk_norm else 0, 1 if v_norm else 0, eps,
+                       q_out.data_ptr(), q_out.stride(0), batch.row_pos.data_ptr(), batch.row_seq.data_ptr(),
+                       batch.seq_slot.data_ptr(), batch.seq_q_start.data_ptr(), batch.seq_q_len.data_ptr(),
+                       block_table.data_ptr(), block_table.stride(0), k_plane.data_ptr(), v_plane.data_ptr(), rows, batch.nseq,
+                       heads, kv_heads, head_dim, value_dim, k_plane.shape[0], block_table.shape[0])
+    _check(_lib.gb_conv_qkv(byref(p), _code(qkv.dtype), _stream()), 2 if taps > 1 else 1)
+
+
+class _SigmoidAttnParams(Structure):
+    _fields_ = _AttnParams._fields_ + [("score_bias", c_void_p), ("gate", c_void_p), ("gate_stride", c_int64)]
+
+
+def attention_sigmoid(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, block_table: torch.Tensor,
+                      batch, heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                      value_dim: Optional[int] = None, score_bias: Optional[torch.Tensor] = None,
+                      gate: Optional[torch.Tensor] = None) -> None:
+    """Causal grouped-query attention over the paged cache with weights sigmoid((q . k) * scale + score_bias[h])
+    that are not normalised over the keys; ``window`` > 0: row i sees keys j with 0 <= i - j < window.  With
+    ``gate`` ([rows, heads] pre-activations, a view with a free row stride) head h's output is multiplied by
+    sigmoid(gate[row, h]).  out is [rows, heads * value_dim]."""
+    a = _attn_params(q, out, k_plane, v_plane, block_table, batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len,
+                     batch.nseq, batch.max_q_len, heads, kv_heads, head_dim, scale, window, 1, None, value_dim)
+    if score_bias is not None:
+        _need(score_bias, "score bias", torch.float32, 1)
+        if score_bias.numel() != heads:
+            raise KernelError(f"attention_sigmoid: score bias of {score_bias.numel()} for {heads} heads")
+    gstride = 0
+    if gate is not None:
+        _need(gate, "head gates", q.dtype, 2, contiguous=False)
+        if gate.shape != (q.shape[0], heads) or gate.stride(1) != 1:
+            raise KernelError(f"attention_sigmoid: gates {tuple(gate.shape)} for {q.shape[0]} rows of {heads} heads")
+        gstride = gate.stride(0)
+    p = _SigmoidAttnParams()
+    for name, _ in _AttnParams._fields_:
+        setattr(p, name, getattr(a, name))
+    p.score_bias = 0 if score_bias is None else score_bias.data_ptr()
+    p.gate = 0 if gate is None else gate.data_ptr()
+    p.gate_stride = gstride
+    _check(_lib.gb_attention_sigmoid(byref(p), _code(q.dtype), _stream()))
+
+
+# ---- mixture of experts -----------------------------------------------------------------------
+class _MoeRouteParams(Structure):
+    _fields_ = [("logits", c_void_p), ("logits_stride", c_int64), ("rows", c_int), ("experts", c_int), ("top", c_int),
+                ("renorm_eps", c_float), ("dense", c_void_p), ("index", c_void_p), ("weight", c_void_p)]
+
+
+class _MoeRowsParams(Structure):
+    _fields_ = [("x", c_void_p), ("x_stride", c_int64), ("up", c_void_p), ("down", c_void_p), ("act", c_void_p), ("out", c_void_p),
+                ("out_stride", c_int64), ("index", c_void_p), ("weight", c_void_p), ("rows", c_int), ("experts", c_int), ("top", c_int),
+                ("ff", c_int), ("hidden", c_int)]
+
+
+def moe_route(logits: torch.Tensor, top: int, renorm_eps: float, dense: torch.Tensor, index: torch.Tensor, weight: torch.Tensor) -> None:
+    """Per row of ``logits`` (float32 [rows, experts]): softmax over the experts, the ``top`` largest scores
+    chosen, their weights s / (sum of the chosen + renorm_eps) left in ``dense`` (float32 [rows, experts], zeros
+    elsewhere) and as pairs in ``index`` (int32 [rows, top]) and ``weight`` (float32 [rows, top])."""
+    _need(logits, "router logits", torch.float32, 2, contiguous=False)
+    rows, experts = logits.shape
+    _need(dense, "expert weights", torch.float32, 2)
+    _need(index, "chosen experts", torch.int32, 2)
+    _need(weight, "chosen weights", torch.float32, 2)
+    if logits.stride(1) != 1 or dense.shape != (rows, experts) or index.shape != (rows, top) or weight.shape != (rows, top):
+        raise KernelError(f"moe_route: logits {tuple(logits.shape)}, dense {tuple(dense.shape)}, pairs {tuple(index.shape)} / {tuple(weight.shape)}")
+    p = _MoeRouteParams(logits.data_ptr(), logits.stride(0), rows, experts, top, renorm_eps, dense.data_ptr(), index.data_ptr(), weight.data_ptr())
+    _check(_lib.gb_moe_route(byref(p), _stream()))
+
+
+def moe_act(up: torch.Tensor, dense: torch.Tensor, act: torch.Tensor, experts: int, ff: int) -> None:
+    """act[r, e * ff + i] = dense[r, e] * relu(up[r, e * ff + i])^2 (``act`` may be ``up``)."""
+    _need(up, "expert pre-activations", dim=2, contiguous=False)
+    _need(act, "expert activations", up.dtype, 2, contiguous=False)
+    _need(dense, "expert weights", torch.float32, 2)
+    rows = up.shape[0]
+    if up.shape != (rows, experts * ff) or act.shape != up.shape or dense.shape != (rows, experts) or up.stride(1) != 1 or act.stride(1) != 1:
+        raise KernelError(f"moe_act: up {tuple(up.shape)}, act {tuple(act.shape)}, weights {tuple(dense.shape)} for {experts} experts of {ff}")
+    _check(_lib.gb_moe_act(_ptr(up), c_int64(up.stride(0)), _ptr(dense), _ptr(act), c_int64(act.stride(0)), c_int(rows), c_int(experts),
+                           c_int(ff), _code(up.dtype), _stream()))
+
+
+def moe_rows(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, index: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+             experts: int, ff: int) -> None:
+    """The experts' feed-forward for a step of few rows, reading only the chosen experts' matrices:
+    out[r] = sum_k weight[r, k] * down_e(relu(up_e x[r])^2), e = index[r, k].  ``up`` is [experts * ff, hidden]
+    (the up matrices one above the other), ``down`` [hidden, experts * ff] (the down matrices side by side),
+    ``out`` float32 [rows, hidden]."""
+    _need(x, "moe x", dim=2, contiguous=False)
+    _need(up, "stacked up matrices", dim=2)
+    _need(down, "stacked down matrices", up.dtype, 2)
+    _need(out, "moe out", torch.float32, 2, contiguous=False)
+    _need(index, "chosen experts", torch.int32, 2)
+    _need(weight, "chosen weights", torch.float32, 2)
+    rows, hidden = x.shape
+    top = index.shape[1]
+    if (up.shape != (experts * ff, hidden) or down.shape != (hidden, experts * ff) or out.shape != (rows, hidden) or x.stride(1) != 1
+            or out.stride(1) != 1 or index.shape[0] != rows or weight.shape != index.shape):
+        raise KernelError(f"moe_rows: x {tuple(x.shape)}, up {tuple(up.shape)}, down {tuple(down.shape)}, out {tuple(out.shape)}")
+    act = torch.empty((rows, top, ff), dtype=x.dtype, device=x.device)
+    p = _MoeRowsParams(x.data_ptr(), x.stride(0), up.data_ptr(), down.data_ptr(), act.data_ptr(), out.data_ptr(), out.stride(0),
+                       index.data_ptr(), weight.data_ptr(), rows, experts, top, ff, hidden)
+    _check(_lib.gb_moe_rows(byref(p), _code(x.dtype), _code(up.dtype), _stream()), 2)

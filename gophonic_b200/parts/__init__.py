@@ -1,13 +1,17 @@
 """The parts a decoder is assembled from, and their registration under their kind names."""
 from .. import registry
-from .base import (FeedForward, KVRequest, Mixer, Norm, Part, PositionEncoding, Runtime, StateRequest,
+from .base import (FeedForward, KVRequest, KVStateRequest, Mixer, Norm, Part, PositionEncoding, Runtime, StateRequest,
                    TensorDecl)
 from .attention import Attention
 from .block import PreNormBlock
+from .delta_rule import DeltaRule
 from .gated_attention import GatedAttention
+from .hyper import HyperBlock
 from .linear_state import DecayState, MatrixMemory
+from .moe import MoE
 from .norm import RMSNorm
 from .rope import NoPosition, PairRotaryEmbedding, RotaryEmbedding
+from .sigmoid_attention import SigmoidAttention
 from .swiglu import SwiGLU
 
 registry.register_norm("rmsnorm", RMSNorm)
@@ -18,8 +22,12 @@ registry.register_mixer("attention", Attention)
 registry.register_mixer("gated_attention", GatedAttention)
 registry.register_mixer("gla", DecayState)
 registry.register_mixer("mlstm", MatrixMemory)
+registry.register_mixer("sigmoid_attention", SigmoidAttention)
+registry.register_mixer("delta_rule", DeltaRule)
 registry.register_feed_forward("swiglu", SwiGLU)
+registry.register_feed_forward("moe", MoE)
 registry.register_block("prenorm", PreNormBlock)
+registry.register_block("hyper", HyperBlock)
 
-__all__ = ["Attention", "DecayState", "FeedForward", "GatedAttention", "MatrixMemory", "PairRotaryEmbedding", "KVRequest", "Mixer", "NoPosition", "Norm", "Part", "PositionEncoding",
+__all__ = ["Attention", "DecayState", "DeltaRule", "FeedForward", "GatedAttention", "HyperBlock", "KVStateRequest", "MatrixMemory", "MoE", "SigmoidAttention", "PairRotaryEmbedding", "KVRequest", "Mixer", "NoPosition", "Norm", "Part", "PositionEncoding",
            "PreNormBlock", "RMSNorm", "RotaryEmbedding", "Runtime", "StateRequest", "SwiGLU", "TensorDecl"]

@@ -10,7 +10,7 @@ A *part* is one of: mixer, feed-forward, norm, position encoding, block.  A part
 * its forward method (see each category below).
 
 A mixer additionally says what it needs from the cache, per sequence:
-``cache_request(spec) -> KVRequest | StateRequest | None`` (classmethod).
+``cache_request(spec) -> KVRequest | StateRequest | KVStateRequest | None`` (classmethod).
 
 No part receives the model or its configuration: sizes and constants arrive in the part's own
 spec.
@@ -28,7 +28,8 @@ class TensorDecl:
     """A tensor a part reads from the checkpoint.
 
     role: "matrix" (projection, [out, in]), "embedding" ([vocab, hidden]), "norm" (a scale
-    vector; initialised near 1), "vector" (initialised near 0), "table" (integers).
+    vector; initialised near 1), "vector" (initialised near 0), "identity" (a small square matrix,
+    initialised near the identity, float32 like a norm's vector), "table" (integers).
     ``optional``: absence is not an error (the tied head).
     """
     name: str
@@ -53,6 +54,15 @@ class StateRequest:
     """Per sequence, fixed size: a tensor of ``shape`` and ``dtype``, zero when a sequence starts."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class KVStateRequest:
+    """Both: keys and values per token and, beside them, a state of fixed size per sequence (a mixer whose
+    keys pass a convolution over time keeps the last projected rows).  The run's view is the key/value
+    view with the state as ``view.state``."""
+    kv: KVRequest
+    state: StateRequest
 
 
 @dataclass

@@ -1,6 +1,7 @@
-"""RMSNorm part: y = x * (1 / sqrt(mean(x^2) + eps)) * weight, plain weight (not 1 + w)
-(internal/qwen3lm/ops.go:251-254; kernels_scalar.go:15-35).  Statistics are fp32; the weight is
-held in fp32 (an exact widening of a bfloat16 checkpoint vector)."""
+"""RMSNorm part: y = x * (1 / sqrt(mean(x^2) + eps)) * weight, plain weight
+(internal/qwen3lm/ops.go:251-254; kernels_scalar.go:15-35), or, where the spec gives an ``offset``, a
+tensor that holds the weight less that offset: y = ... * (offset + w).  Statistics are fp32; the weight is held in fp32
+(an exact widening of a bfloat16 checkpoint vector, the offset added in fp32)."""
 from __future__ import annotations
 
 from typing import List, Mapping, Optional
@@ -15,12 +16,17 @@ class RMSNorm(Norm):
 
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
-        return [TensorDecl(prefix + getattr(spec, "tensor", "weight"), (spec.size,), role="norm")]
+        # a tensor that holds a difference from the offset is initialised near zero
+        role = "vector" if float(getattr(spec, "offset", 0.0)) != 0.0 else "norm"
+        return [TensorDecl(prefix + getattr(spec, "tensor", "weight"), (spec.size,), role=role)]
 
     def __init__(self, spec, prefix: str, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         self.spec = spec
         self.rt = runtime
         self.weight = tensors[prefix + getattr(spec, "tensor", "weight")].to(torch.float32).contiguous()
+        offset = float(getattr(spec, "offset", 0.0))
+        if offset != 0.0:
+            self.weight = (self.weight + offset).contiguous()
         self.eps = float(spec.eps)
 
     def rms_fold(self):

@@ -118,8 +118,10 @@ def read_config(model_dir: str):
 def _register_builtin() -> None:
     from .config.qwen3 import Qwen3Config
     from .config.pugalix import PugalixConfig
+    from .config.vepitar import VepitarConfig
     register_architecture("Qwen3ForCausalLM", Qwen3Config, model_type="qwen3")
     register_architecture("Pugalix", PugalixConfig)
+    register_architecture("Vepitar", VepitarConfig)
 
 
 _register_builtin()

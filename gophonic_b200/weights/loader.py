@@ -92,7 +92,7 @@ def place(t: torch.Tensor, stored: str, role: str, mode: str, device) -> torch.T
     if role == "table":
         return t.to(device=device, dtype=torch.int32)
     t = t.to(device)
-    if role in ("norm",) or mode == "float32":
+    if role in ("norm", "identity") or mode == "float32":
         return t.to(torch.float32)
     if stored == "F32":
         return t
@@ -114,7 +114,7 @@ def load_tensors(model_dir: str, decls: Sequence[TensorDecl], mode: str, device,
                 continue
             e = ckpt.tensors[d.name]
             arr = ckpt.read(d.name)
-            if d.role == "norm":
+            if d.role in ("norm", "identity"):
                 vals = arr if e.dtype != "BF16" else (arr.astype(np.uint32) << np.uint32(16)).view(np.float32)
                 if not np.all(np.isfinite(vals)):
                     raise CheckpointError(f"{d.name} holds a non-finite value")

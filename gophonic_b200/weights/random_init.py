@@ -46,6 +46,8 @@ def _tensor_seed(seed: int, name: str) -> int:
 def _std_and_mean(d: TensorDecl, scales: InitScales, head_name: Optional[str]):
     if d.role == "norm":
         return scales.norm, 1.0
+    if d.role == "identity":           # a square matrix near the identity: the fill around zero, then one added on the diagonal
+        return scales.norm, 0.0
     if d.role == "embedding":
         return scales.embedding, 0.0
     if head_name is not None and d.name == head_name:
@@ -109,7 +111,10 @@ def random_tensor(d: TensorDecl, seed: int, scales: InitScales, head_name: Optio
     """fp32 values of one declared tensor."""
     std, mean = _std_and_mean(d, scales, head_name)
     _sized(d)
-    return counter_fill(_tensor_seed(seed, d.name), int(np.prod(d.shape)), std, mean).reshape(d.shape)
+    vals = counter_fill(_tensor_seed(seed, d.name), int(np.prod(d.shape)), std, mean).reshape(d.shape)
+    if d.role == "identity":
+        vals += np.eye(d.shape[0], d.shape[1], dtype=np.float32)
+    return vals
 
 
 def write_random_model(config, seed: int, out_dir: str, weight_dtype: str = "bfloat16",
@@ -166,5 +171,10 @@ def random_tensors_on_device(spec, seed: int, mode: str, device, scales: InitSca
         _sized(d)
         t = torch.empty(d.shape, dtype=torch.bfloat16, device=device)   # what a BF16 checkpoint stores
         ops.random_fill(t, _tensor_seed(seed, d.name), float(fill_constant(std)), float(mean))
+        if d.role == "identity":
+            # the file's values: the fp32 fill plus one on the diagonal, rounded once
+            f = torch.empty(d.shape, dtype=torch.float32, device=device)
+            ops.random_fill(f, _tensor_seed(seed, d.name), float(fill_constant(std)), float(mean))
+            t = (f + torch.eye(d.shape[0], d.shape[1], dtype=torch.float32, device=device)).to(torch.bfloat16)
         out[d.name] = place(t, "BF16", d.role, mode, device)
     return out

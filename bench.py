@@ -280,10 +280,13 @@ def further_model_points(name, steps, torch, ops, hbm_peak, tflops_peak):
 
 
 # ---- another design beside its closest model ---------------------------------------------------
-DESIGN_TWINS = {"pugalix-2k": "1.7b", "pugalix-4k": "8b"}      # the same width, heads, head size, feed-forward and vocabulary
+# the same width, heads, head size, feed-forward and vocabulary (a Vepitar configuration beside the Pugalix one of its width:
+# both mix matrix-state layers with windowed attention)
+DESIGN_TWINS = {"pugalix-2k": "1.7b", "pugalix-4k": "8b", "vepitar-2k": "pugalix-2k", "vepitar-4k": "pugalix-4k"}
 OP_CLASSES = ("gemm", "gemm_add", "gemm_swiglu", "gemm_scaled", "gemm_residual", "attention", "attention_decode_rope",
               "qk_norm_rope_kv_write", "state_scan", "head_norm_gate", "gla_decay", "add_rmsnorm", "embed_gather", "swiglu",
-              "prenorm_layer_forward")
+              "prenorm_layer_forward", "delta_scan", "conv_qkv", "attention_sigmoid", "hyper_mix_norm", "moe_route", "moe_act", "moe_rows",
+              "moe_group", "moe_gather", "moe_combine", "relu2", "tanh_")
 
 
 class OpTimer:
@@ -295,7 +298,9 @@ class OpTimer:
 
     def __enter__(self):
         for name in OP_CLASSES:
-            fn = getattr(self.ops, name)
+            fn = getattr(self.ops, name, None)
+            if fn is None:
+                continue
             self.saved[name] = fn
 
             def timed(*a, _fn=fn, _name=name, **k):

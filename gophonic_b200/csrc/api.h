@@ -143,6 +143,8 @@ GB_API int gb_gemm_tc5_pair(const void* A, const void* W, void* C, int c_dtype, 
                             cudaStream_t stream);
 GB_API int gb_gemm_tc5_pair_swiglu(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc,
                                    cudaStream_t stream);
+GB_API int gb_gemm_tc5_ldw(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                           int pair, cudaStream_t stream);
 GB_API int gb_gemm_tc5_pair_add(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream);
 // most rows the products with the residual's row-wise work folded in take
 constexpr int GB_FOLD_MAX_ROWS = 64;
@@ -205,10 +207,12 @@ struct DeltaStateParams {
     float* remove;          // [rows, remove_stride]: heads x d pre-activations of the removal rate; a * u afterwards
     int64_t remove_stride;
     const float* remove_bias;
-    float* unit;            // [rows, unit_stride]: heads x d, receives the unit keys
-    int64_t unit_stride;
+    const float* low;       // single tokens only, or null: [rows, low_stride] holding `rank` numbers whose tanh, times w2, is the
+    int64_t low_stride;     // decay's pre-activation (decay is then not read)
+    const void* w2;         // [heads * d, rank]
+    int rank;
     float key_eps;          // under the root of the key's length
-    float* dots;            // [rows, heads, 2]: receives (a u) . r and k . r
+    float* dots;            // [rows, heads, 4] scratch for rows of more than one token: (a u) . r, k . r, 1 / |k|
     float* state;           // [slots, ...]: per head d x dv
     int64_t slot_stride, head_stride;
     float* out;             // [rows, out_stride]: heads x dv sums S^T r
@@ -220,8 +224,9 @@ struct DeltaStateParams {
     int max_slots;
     int max_q_len;          // most rows a sequence brings; 1 selects the kernel for single tokens
 };
-GB_API int gb_delta_scan(const DeltaStateParams* p, int dtype, cudaStream_t stream);
-GB_API int gb_tanh(float* z, int64_t n, cudaStream_t stream);
+GB_API int gb_delta_scan(const DeltaStateParams* p, int dtype, int w2_dtype, cudaStream_t stream);
+GB_API int gb_delta_fused_max_rank();
+GB_API int gb_tanh(float* z, int rows, int cols, int64_t stride, cudaStream_t stream);
 
 // Short causal convolution over time on the projected q | k | v, head norms, q out and k, v into the cache.
 struct ConvQkvParams {
@@ -246,6 +251,7 @@ struct ConvQkvParams {
     void* v_plane;
     int rows, nseq, heads, kv_heads, d, dv;
     int pages, max_slots;
+    int max_q_len;          // most rows a sequence brings; 1: the row-wise kernel moves the state on itself
 };
 GB_API int gb_conv_qkv(const ConvQkvParams* p, int dtype, cudaStream_t stream);
 
@@ -283,3 +289,8 @@ struct MoeRowsParams {
     int rows, experts, top, ff, hidden;
 };
 GB_API int gb_moe_rows(const MoeRowsParams* p, int dtype, int w_dtype, cudaStream_t stream);
+GB_API int gb_moe_group(const int* index, int rows, int top, int experts, int* offsets, int* place, int* src_row, cudaStream_t stream);
+GB_API int gb_moe_gather(const void* x, int64_t x_stride, const int* src_row, void* xs, int pairs, int hidden, int dtype, cudaStream_t stream);
+GB_API int gb_relu2(void* z, int64_t n, int dtype, cudaStream_t stream);
+GB_API int gb_moe_combine(const float* ys, const int* place, const float* weight, float* out, int64_t out_stride, int rows, int top, int hidden,
+                          cudaStream_t stream);

@@ -13,14 +13,201 @@
 // the softmax kernel on the CUDA cores does; keys are visited in tiles of 32 that start at absolute
 // positions 0, 32, 64, ..., and every weight is independent of the others, so a row's result does not
 // depend on how its sequence was cut into steps or on what else is in the batch.
+//
+// In bfloat16, with key and value heads of whole 16s up to 128, the same sum runs on mma.sync tensor cores:
+// a CTA owns 64 query rows of one head of one sequence (16 rows a warp) and walks the pages its rows can see,
+// a page of 64 keys fetched with cp.async one page ahead of the arithmetic; the weights are formed in fp32
+// from the fp32 scores, rounded to bfloat16 for the second product (the values are bfloat16), and summed in
+// fp32.  Prompts, portions and single tokens take the same kernel.
 #include "api.h"
-#include "common.cuh"
+#include "mma.cuh"
 
 #include <math.h>
 
 namespace {
 
 constexpr int MAX_TAPS = 8;
+typedef __nv_bfloat16 bf16;
+constexpr float LOG2E = 1.4426950408889634f;
+
+// copy 64 rows of N bf16 (contiguous in global memory) into padded shared rows
+template <int N>
+__device__ __forceinline__ void load_page(bf16* dst, const bf16* src, int tid, int nthreads) {
+    constexpr int SD = N + 8, CH = N / 8;
+    for (int idx = tid; idx < 64 * CH; idx += nthreads) {
+        int row = idx / CH, c = idx - row * CH;
+        cp_async16(dst + row * SD + c * 8, src + row * N + c * 8, 16);
+    }
+}
+
+template <int HD, int DV>
+__global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(SigmoidAttnParams p) {
+    constexpr int SD = HD + 8, SV = DV + 8, KS = HD / 16, NF = DV / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Ks = Qs + 64 * SD;
+    bf16* Vs = Ks + 2 * 64 * SD;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int q_len = p.seq_q_len[seq], kv_len = p.seq_kv_len[seq];
+    const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;  // late (long) tiles first
+    const int q0 = qt * 64;
+    if (q0 >= q_len) return;
+    const int past = kv_len - q_len;
+    const int q_start = p.seq_q_start[seq];
+    const int G = p.heads / p.kv_heads, kvh = head / G;
+    const int* bt = block_table_row(p.block_table, p.bt_stride, p.seq_slot[seq], p.max_slots);
+    const bf16* kbase = (const bf16*)p.k_plane;
+    const bf16* vbase = (const bf16*)p.v_plane;
+
+    {
+        constexpr int CH = HD / 8;
+        const bf16* qsrc = (const bf16*)p.q + (int64_t)(q_start + q0) * p.q_row_stride + (int64_t)head * HD;
+        for (int idx = tid; idx < 64 * CH; idx += 128) {
+            int row = idx / CH, c = idx - row * CH;
+            bool ok = q0 + row < q_len;
+            cp_async16(Qs + row * SD + c * 8, ok ? qsrc + (int64_t)row * p.q_row_stride + c * 8 : qsrc, ok ? 16 : 0);
+        }
+    }
+    const int last_q = (q0 + 64 < q_len ? q0 + 64 : q_len) - 1;
+    const int hi_pos = past + last_q;
+    int lo_pos = 0;
+    if (p.window > 0) {
+        lo_pos = past + q0 - p.window + 1;
+        if (lo_pos < 0) lo_pos = 0;
+    }
+    const int t_lo = lo_pos / 64, t_hi = hi_pos / 64;
+    const int n_tiles = t_hi - t_lo + 1;
+
+    auto load_tile = [&](int t, int buf) {
+        int64_t page = page_of(bt, t * 64, p.bt_stride, p.pages);
+        int64_t at = (page * p.kv_heads + kvh) * 64;
+        load_page<HD>(Ks + buf * 64 * SD, kbase + at * HD, tid, 128);
+        load_page<DV>(Vs + buf * 64 * SV, vbase + at * DV, tid, 128);
+    };
+    load_tile(t_lo, 0);
+    cp_async_commit();
+
+    const float sc = p.scale * LOG2E;
+    const float bias = (p.score_bias ? p.score_bias[head] : 0.f) * LOG2E;
+    const int row0 = past + q0 + warp * 16 + g;  // absolute position of this thread's first row
+    const int row1 = row0 + 8;
+    float o[NF][4];
+#pragma unroll
+    for (int j = 0; j < NF; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[j][e] = 0.f;
+    uint32_t qf[KS][4];
+
+    for (int ti = 0; ti < n_tiles; ti++) {
+        const int t = t_lo + ti;
+        const int buf = ti & 1;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (ti + 1 < n_tiles) load_tile(t + 1, buf ^ 1);
+        cp_async_commit();
+        if (ti == 0) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++)
+                ldmatrix_x4(qf[ks], Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks * 16 + (lane >> 4) * 8);
+        }
+        const bf16* kt = Ks + buf * 64 * SD;
+        const bf16* vt = Vs + buf * 64 * SV;
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) s[j][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+#pragma unroll
+            for (int jp = 0; jp < 4; jp++) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kt + (jp * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_bf16_16816(s[jp * 2], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b[0], b[1]);
+                mma_bf16_16816(s[jp * 2 + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b[2], b[3]);
+            }
+        }
+        // the weights: sigmoid(score * scale + bias) where the key is visible, by absolute position
+        uint32_t pa[4][4];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                int key = t * 64 + j * 8 + t4 * 2 + (e & 1);
+                int row = (e & 2) ? row1 : row0;
+                bool ok = key <= row && (p.window <= 0 || key > row - p.window);
+                w[e] = ok ? __fdividef(1.f, 1.f + exp2f(-fmaf(s[j][e], sc, bias))) : 0.f;
+            }
+            pa[j >> 1][(j & 1) * 2] = pack_bf16(w[0], w[1]);
+            pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(w[2], w[3]);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) {
+#pragma unroll
+            for (int c = 0; c < DV / 16; c++) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SV + c * 16 + (lane >> 4) * 8);
+                mma_bf16_16816(o[c * 2], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[0], b[1]);
+                mma_bf16_16816(o[c * 2 + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[2], b[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;
+    bf16* ob = (bf16*)p.out + (int64_t)head * DV;
+    const bf16* gate = (const bf16*)p.gate;
+    if (r0 < q_len) {
+        const int64_t row = q_start + r0;
+        const float gv = gate ? 1.f / (1.f + expf(-__bfloat162float(gate[row * p.gate_stride + head]))) : 1.f;
+        bf16* op = ob + row * p.out_row_stride;
+#pragma unroll
+        for (int j = 0; j < NF; j++) *reinterpret_cast<uint32_t*>(op + j * 8 + t4 * 2) = pack_bf16(o[j][0] * gv, o[j][1] * gv);
+    }
+    if (r1 < q_len) {
+        const int64_t row = q_start + r1;
+        const float gv = gate ? 1.f / (1.f + expf(-__bfloat162float(gate[row * p.gate_stride + head]))) : 1.f;
+        bf16* op = ob + row * p.out_row_stride;
+#pragma unroll
+        for (int j = 0; j < NF; j++) *reinterpret_cast<uint32_t*>(op + j * 8 + t4 * 2) = pack_bf16(o[j][2] * gv, o[j][3] * gv);
+    }
+}
+
+template <int HD, int DV>
+int launch_mma_dv(const SigmoidAttnParams& p, cudaStream_t stream) {
+    const size_t smem = (size_t)(3 * 64 * (HD + 8) + 2 * 64 * (DV + 8)) * sizeof(bf16);
+    static bool configured = false;
+    if (!configured && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attn_sigmoid_mma_kernel<HD, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) GB_REFUSE("attention_sigmoid: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(ceil_div(p.max_q_len, 64), p.heads, p.nseq);
+    if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("attention_sigmoid: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);
+    attn_sigmoid_mma_kernel<HD, DV><<<grid, 128, smem, stream>>>(p);
+    GB_CHECK_LAUNCH("attention_sigmoid_mma");
+    return 0;
+}
+
+template <int HD>
+int launch_mma(const SigmoidAttnParams& p, int dv, cudaStream_t stream) {
+    switch (dv) {
+        case 32: return launch_mma_dv<HD, 32>(p, stream);
+        case 48: return launch_mma_dv<HD, 48>(p, stream);
+        case 64: return launch_mma_dv<HD, 64>(p, stream);
+        case 128: return launch_mma_dv<HD, 128>(p, stream);
+    }
+    return 1;
+}
+
+// whether the tensor-core kernel takes these sizes and pointers
+bool mma_takes(const SigmoidAttnParams& p, int dv) {
+    const bool hd = p.d == 32 || p.d == 64 || p.d == 96 || p.d == 128;
+    const bool vd = dv == 32 || dv == 48 || dv == 64 || dv == 128;
+    return hd && vd && !(p.q_row_stride & 7) && !((uintptr_t)p.q & 15) && !(p.out_row_stride & 1) && !((uintptr_t)p.out & 3);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(128) conv_qkv_kernel(ConvQkvParams p) {
@@ -35,7 +222,8 @@ __global__ void __launch_bounds__(128) conv_qkv_kernel(ConvQkvParams p) {
     const T* base = (const T*)p.qkv;
     const float* state = p.state ? p.state + (int64_t)slot * p.state_slot_stride : nullptr;
     const int n_heads = p.heads + 2 * p.kv_heads;
-    for (int hh = warp; hh < n_heads; hh += 4) {
+    const bool move_state = taps > 1 && p.max_q_len == 1;     // single tokens: this thread also moves its channels' state on
+    for (int hh = blockIdx.y * 4 + warp; hh < n_heads; hh += 4 * gridDim.y) {
         // which head: query heads, then key heads, then value heads
         int c0, n, kind;
         if (hh < p.heads)
@@ -64,6 +252,8 @@ __global__ void __launch_bounds__(128) conv_qkv_kernel(ConvQkvParams p) {
                     else
                         uv = state[(int64_t)(back_max + t_in - back) * p.channels + ch];
                     a = fmaf(p.conv_w[(int64_t)ch * taps + j], uv, a);
+                    // the value tap j read is what the state's row j - 1 holds after this token
+                    if (move_state && j > 0) p.state[(int64_t)slot * p.state_slot_stride + (int64_t)(j - 1) * p.channels + ch] = uv;
                 }
                 y[e] = a;
             }
@@ -284,9 +474,12 @@ int launch(const SigmoidAttnParams& p, cudaStream_t stream) {
 
 template <typename T>
 int launch_conv(const ConvQkvParams& p, cudaStream_t stream) {
-    conv_qkv_kernel<T><<<p.rows, 128, 0, stream>>>(p);
+    const int n_heads = p.heads + 2 * p.kv_heads;
+    int chunks = 1;                       // few rows: the heads of a row are spread over several CTAs
+    while (chunks * 4 < n_heads && p.rows * chunks < 296) chunks++;
+    conv_qkv_kernel<T><<<dim3(p.rows, chunks), 128, 0, stream>>>(p);
     GB_CHECK_LAUNCH("conv_qkv");
-    if (p.taps > 1) {
+    if (p.taps > 1 && p.max_q_len != 1) {
         dim3 grid(ceil_div(p.channels, 128), p.nseq);
         if (grid.y > 65535) GB_REFUSE("conv_qkv: %d sequences exceed one launch", p.nseq);
         conv_state_update_kernel<T><<<grid, 128, 0, stream>>>(p);
@@ -320,6 +513,15 @@ GB_API int gb_attention_sigmoid(const SigmoidAttnParams* pp, int dtype, cudaStre
     if (p.window < 0) GB_REFUSE("attention: window %d", p.window);
     if (p.dv < 0 || p.dv > 256) GB_REFUSE("attention_sigmoid: value size %d is outside [1, 256]", p.dv);
     if (dtype == GB_F32) return launch<float>(p, stream);
+    const int dv = p.dv > 0 ? p.dv : p.d;
+    if (dtype == GB_BF16 && p.num_splits != -1 && mma_takes(p, dv)) {     // num_splits -1 asks for the CUDA-core kernel
+        switch (p.d) {
+            case 32: return launch_mma<32>(p, dv, stream);
+            case 64: return launch_mma<64>(p, dv, stream);
+            case 96: return launch_mma<96>(p, dv, stream);
+            case 128: return launch_mma<128>(p, dv, stream);
+        }
+    }
     if (dtype == GB_BF16) return launch<__nv_bfloat16>(p, stream);
     GB_REFUSE("attention: unknown dtype %d", dtype);
 }

@@ -513,7 +513,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_pair_kernel(const __grid_con
 }
 
 template <typename TC>
-int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, int epi, cudaStream_t stream) {
+int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int epi, cudaStream_t stream) {
     const int smem = PAIR_STAGES * PAIR_STAGE_BYTES + PAIR_STAGING_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
@@ -523,7 +523,7 @@ int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int6
     }
     CUtensorMap map_a, map_w, map_c;
     if (int rc = tc5_make_map(&map_a, A, M, K, lda, 128)) return rc;
-    if (int rc = tc5_make_map(&map_w, W, N, K, K, 128)) return rc;
+    if (int rc = tc5_make_map(&map_w, W, N, K, ldw, 128)) return rc;
     memset(&map_c, 0, sizeof(map_c));
     if (epi == 2) {
         // float32 C in boxes of 32 x 32, 128-byte swizzle, for the epilogue's TMA reductions
@@ -554,7 +554,7 @@ int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int6
 }
 
 template <typename TC>
-int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, int epi, cudaStream_t stream) {
+int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int epi, cudaStream_t stream) {
     const int smem = STAGES * STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
@@ -564,7 +564,7 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t l
     }
     CUtensorMap map_a, map_w;
     if (int rc = tc5_make_map(&map_a, A, M, K, lda, BM)) return rc;
-    if (int rc = tc5_make_map(&map_w, W, N, K, K, BN)) return rc;
+    if (int rc = tc5_make_map(&map_w, W, N, K, ldw, BN)) return rc;
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -582,8 +582,10 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t l
 }  // namespace
 
 static int tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc, int epi, int pair,
-               cudaStream_t stream) {
+               cudaStream_t stream, int64_t ldw = 0) {
     if (M <= 0 || N <= 0) return 0;
+    if (ldw == 0) ldw = K;
+    if ((ldw & 7) || ldw < K) GB_REFUSE("gemm_tc5: row stride %lld of W must be a multiple of 8 and at least K", (long long)ldw);
     if (K <= 0 || (K & 7)) GB_REFUSE("gemm_tc5: K = %d must be a positive multiple of 8", K);
     if ((lda & 7) || lda < K) GB_REFUSE("gemm_tc5: row stride %lld of A must be a multiple of 8 and at least K", (long long)lda);
     if ((epi == 0 || epi == 2) && ldc < N) GB_REFUSE("gemm_tc5: row stride %lld of C is shorter than N = %d", (long long)ldc, N);
@@ -591,11 +593,11 @@ static int tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N,
     if (epi == 1 && ((N & 15) || ldc < N / 2)) GB_REFUSE("gemm_tc5: the SwiGLU epilogue needs N = %d to be a multiple of 16", N);
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_tc5: operands must be 16-byte aligned");
     if (pair) {
-        if (c_dtype == GB_F32) return launch_pair<float>(A, W, C, M, N, K, lda, ldc, epi, stream);
-        if (c_dtype == GB_BF16) return launch_pair<__nv_bfloat16>(A, W, C, M, N, K, lda, ldc, epi, stream);
+        if (c_dtype == GB_F32) return launch_pair<float>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+        if (c_dtype == GB_BF16) return launch_pair<__nv_bfloat16>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
     } else {
-        if (c_dtype == GB_F32) return launch<float>(A, W, C, M, N, K, lda, ldc, epi, stream);
-        if (c_dtype == GB_BF16) return launch<__nv_bfloat16>(A, W, C, M, N, K, lda, ldc, epi, stream);
+        if (c_dtype == GB_F32) return launch<float>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+        if (c_dtype == GB_BF16) return launch<__nv_bfloat16>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
     }
     GB_REFUSE("gemm_tc5: unknown output dtype %d", c_dtype);
 }
@@ -603,6 +605,13 @@ static int tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N,
 GB_API int gb_gemm_tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc,
                        cudaStream_t stream) {
     return tc5(A, W, C, c_dtype, M, N, K, lda, ldc, 0, 0, stream);
+}
+
+// The same product with a weight matrix whose rows lie ldw elements apart (a block of columns of a wider matrix);
+// pair: the kernel that pairs two SMs on a tile.
+GB_API int gb_gemm_tc5_ldw(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
+                           int pair, cudaStream_t stream) {
+    return tc5(A, W, C, c_dtype, M, N, K, lda, ldc, 0, pair, stream, ldw);
 }
 
 // The same product with tiles of 256 x 256 on pairs of SMs (tcgen05.mma.cta_group::2).

@@ -13,6 +13,12 @@
 //
 // moe_up_rows / moe_down_rows: the same feed-forward for a step of few rows, reading only the chosen
 // experts' matrices (a warp a hidden unit, or an output column, of one (row, choice) pair).
+//
+// moe_group / moe_gather / relu2 / moe_combine: a step of many rows sorts its (row, choice) pairs by expert
+// (counts, offsets, and each pair's place in the sorted order), gathers the rows in that order so that every
+// expert's rows lie together for one product an expert, squares the positive part between the two products, and
+// adds each row's `top` results up with their weights in the order of the choices.  Where a pair lands inside its
+// expert's group may differ from run to run; a row's result does not depend on it.
 #include "api.h"
 #include "common.cuh"
 
@@ -95,6 +101,34 @@ __global__ void moe_act_kernel(const T* __restrict__ up, int64_t up_stride, cons
     act[r * act_stride + c] = from_f32<T>(w * z * z);
 }
 
+// a warp's share of the dot product of a weight row and a row of activations, 16 bytes a lane where both allow it
+template <typename T, typename TW>
+__device__ __forceinline__ float warp_dot(const TW* __restrict__ w, const T* __restrict__ x, int n, int lane) {
+    float a = 0.f;
+    for (int c = lane; c < n; c += 32) a = fmaf(to_f32<TW>(w[c]), to_f32<T>(x[c]), a);
+    return a;
+}
+template <>
+__device__ __forceinline__ float warp_dot<__nv_bfloat16, __nv_bfloat16>(const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ x,
+                                                                        int n, int lane) {
+    float a = 0.f;
+    if (!(n & 7) && !((uintptr_t)w & 15) && !((uintptr_t)x & 15)) {
+        for (int c = lane * 8; c < n; c += 256) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(w + c), xv = *reinterpret_cast<const uint4*>(x + c);
+            const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+            const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                a = fmaf(__low2float(wh[e]), __low2float(xh[e]), a);
+                a = fmaf(__high2float(wh[e]), __high2float(xh[e]), a);
+            }
+        }
+        return a;
+    }
+    for (int c = lane; c < n; c += 32) a = fmaf(__bfloat162float(w[c]), __bfloat162float(x[c]), a);
+    return a;
+}
+
 // few rows: act[r, k, i] = weight[r, k] * relu(W_up[index[r, k]][i, :] . x[r])^2, a warp a hidden unit
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128) moe_up_rows_kernel(MoeRowsParams p) {
@@ -106,9 +140,7 @@ __global__ void __launch_bounds__(128) moe_up_rows_kernel(MoeRowsParams p) {
     const int e = p.index[pair];
     const TW* w = (const TW*)p.up + ((int64_t)e * p.ff + i) * p.hidden;
     const T* x = (const T*)p.x + (int64_t)r * p.x_stride;
-    float a = 0.f;
-    for (int c = lane; c < p.hidden; c += 32) a = fmaf(to_f32<TW>(w[c]), to_f32<T>(x[c]), a);
-    a = warp_sum(a);
+    const float a = warp_sum(warp_dot<T, TW>(w, x, p.hidden, lane));
     if (lane == 0) {
         // the same roundings as the stacked path: the product in the activation dtype, then the activation
         const float z = fmaxf(to_f32<T>(from_f32<T>(a)), 0.f);
@@ -128,14 +160,117 @@ __global__ void __launch_bounds__(128) moe_down_rows_kernel(MoeRowsParams p) {
         const int pair = r * p.top + k;
         const int e = p.index[pair];
         const TW* w = (const TW*)p.down + ((int64_t)c * p.experts + e) * p.ff;      // the down matrices side by side: [hidden, experts * ff]
-        const T* z = (const T*)p.act + (int64_t)pair * p.ff;
-        for (int i = lane; i < p.ff; i += 32) a = fmaf(to_f32<TW>(w[i]), to_f32<T>(z[i]), a);
+        a += warp_dot<T, TW>(w, (const T*)p.act + (int64_t)pair * p.ff, p.ff, lane);
     }
     a = warp_sum(a);
     if (lane == 0) p.out[(int64_t)r * p.out_stride + c] = a;
 }
 
+constexpr int GROUP_THREADS = 1024;
+constexpr int GROUP_MAX_EXPERTS = 512;
+
+// one CTA: counts of the pairs of each expert, offsets of the experts' groups, and a place in its group for every pair
+__global__ void __launch_bounds__(GROUP_THREADS) moe_group_kernel(const int* __restrict__ index, int pairs, int top, int experts,
+                                                                 int* __restrict__ offsets, int* __restrict__ place, int* __restrict__ src_row) {
+    __shared__ int count[GROUP_MAX_EXPERTS], cursor[GROUP_MAX_EXPERTS];
+    const int tid = threadIdx.x;
+    for (int e = tid; e < experts; e += GROUP_THREADS) count[e] = 0;
+    __syncthreads();
+    for (int i = tid; i < pairs; i += GROUP_THREADS) atomicAdd(&count[index[i]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; e++) {
+            offsets[e] = at;
+            cursor[e] = at;
+            at += count[e];
+        }
+        offsets[experts] = at;
+    }
+    __syncthreads();
+    for (int i = tid; i < pairs; i += GROUP_THREADS) {
+        const int at = atomicAdd(&cursor[index[i]], 1);
+        place[i] = at;
+        src_row[at] = i / top;
+    }
+}
+
+// xs[p, :] = x[src_row[p], :], 16 bytes a thread where rows allow it
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, int64_t x_stride, const int* __restrict__ src_row, T* __restrict__ xs, int hidden) {
+    const int64_t p = blockIdx.x;
+    const T* src = x + (int64_t)src_row[p] * x_stride;
+    T* dst = xs + p * hidden;
+    constexpr int V = 16 / sizeof(T);
+    if (!(hidden % V) && !(x_stride % V) && !((uintptr_t)x & 15) && !((uintptr_t)xs & 15)) {
+        for (int c = threadIdx.x; c < hidden / V; c += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = src[c];
+    }
+}
+
+template <typename T>
+__global__ void relu2_kernel(T* __restrict__ z, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = fmaxf(to_f32<T>(z[i]), 0.f);
+    z[i] = from_f32<T>(v * v);
+}
+
+// out[r, :] = sum_k weight[r, k] * ys[place[r * top + k], :], in the order of k
+__global__ void moe_combine_kernel(const float* __restrict__ ys, const int* __restrict__ place, const float* __restrict__ weight,
+                                   float* __restrict__ out, int64_t out_stride, int top, int hidden) {
+    const int64_t r = blockIdx.x;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float a = 0.f;
+        for (int k = 0; k < top; k++) a = fmaf(weight[r * top + k], ys[(int64_t)place[r * top + k] * hidden + c], a);
+        out[r * out_stride + c] = a;
+    }
+}
+
 }  // namespace
+
+GB_API int gb_moe_group(const int* index, int rows, int top, int experts, int* offsets, int* place, int* src_row, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (experts <= 0 || experts > GROUP_MAX_EXPERTS || top <= 0) GB_REFUSE("moe_group: %d experts, %d a token", experts, top);
+    moe_group_kernel<<<1, GROUP_THREADS, 0, stream>>>(index, rows * top, top, experts, offsets, place, src_row);
+    GB_CHECK_LAUNCH("moe_group");
+    return 0;
+}
+
+GB_API int gb_moe_gather(const void* x, int64_t x_stride, const int* src_row, void* xs, int pairs, int hidden, int dtype, cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    if (dtype == GB_F32)
+        moe_gather_kernel<float><<<pairs, 128, 0, stream>>>((const float*)x, x_stride, src_row, (float*)xs, hidden);
+    else if (dtype == GB_BF16)
+        moe_gather_kernel<__nv_bfloat16><<<pairs, 128, 0, stream>>>((const __nv_bfloat16*)x, x_stride, src_row, (__nv_bfloat16*)xs, hidden);
+    else
+        GB_REFUSE("moe_gather: unknown dtype %d", dtype);
+    GB_CHECK_LAUNCH("moe_gather");
+    return 0;
+}
+
+GB_API int gb_relu2(void* z, int64_t n, int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (dtype == GB_F32)
+        relu2_kernel<float><<<blocks, 256, 0, stream>>>((float*)z, n);
+    else if (dtype == GB_BF16)
+        relu2_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)z, n);
+    else
+        GB_REFUSE("relu2: unknown dtype %d", dtype);
+    GB_CHECK_LAUNCH("relu2");
+    return 0;
+}
+
+GB_API int gb_moe_combine(const float* ys, const int* place, const float* weight, float* out, int64_t out_stride, int rows, int top, int hidden,
+                          cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    moe_combine_kernel<<<rows, 256, 0, stream>>>(ys, place, weight, out, out_stride, top, hidden);
+    GB_CHECK_LAUNCH("moe_combine");
+    return 0;
+}
 
 GB_API int gb_moe_route(const MoeRouteParams* pp, cudaStream_t stream) {
     MoeRouteParams p = *pp;

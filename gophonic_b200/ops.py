@@ -985,23 +985,29 @@ class _DeltaStateParams(Structure):
         ("rkv", c_void_p), ("row_stride", c_int64), ("r_off", c_int), ("k_off", c_int), ("v_off", c_int),
         ("decay", c_void_p), ("decay_stride", c_int64), ("decay_bias", c_void_p), ("decay_scale", c_float),
         ("remove", c_void_p), ("remove_stride", c_int64), ("remove_bias", c_void_p),
-        ("unit", c_void_p), ("unit_stride", c_int64), ("key_eps", c_float), ("dots", c_void_p),
+        ("low", c_void_p), ("low_stride", c_int64), ("w2", c_void_p), ("rank", c_int), ("key_eps", c_float), ("dots", c_void_p),
         ("state", c_void_p), ("slot_stride", c_int64), ("head_stride", c_int64), ("out", c_void_p), ("out_stride", c_int64),
         ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
         ("rows", c_int), ("nseq", c_int), ("heads", c_int), ("d", c_int), ("dv", c_int), ("max_slots", c_int), ("max_q_len", c_int),
     ]
 
 
-def delta_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, heads: int, d: int, dv: int, decay: torch.Tensor,
+DELTA_FUSED_MAX_RANK = int(_lib.gb_delta_fused_max_rank())   # largest rank of the decay's projection a single-token step folds in
+
+
+def delta_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, heads: int, d: int, dv: int, decay: Optional[torch.Tensor],
                decay_bias: Optional[torch.Tensor], decay_scale: float, remove: torch.Tensor, remove_bias: Optional[torch.Tensor],
                key_eps: float, state: torch.Tensor, out: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
-               seq_q_len: torch.Tensor, nseq: int, max_q_len: int = 0) -> None:
+               seq_q_len: torch.Tensor, nseq: int, max_q_len: int = 0, low: Optional[torch.Tensor] = None,
+               w2: Optional[torch.Tensor] = None) -> None:
     """The generalized delta rule over the rows of a step, token by token, for every (sequence, head):
     S <- diag(w) S - (a u)(u^T S) + k v^T from the old S, o = S^T r, with u the key over its length
-    (``key_eps`` under the root).  ``decay`` and ``remove`` (float32 [rows, heads * d]) hold pre-activations and
-    are overwritten: w = exp(-decay_scale * sigmoid(decay + decay_bias)), a = sigmoid(remove + remove_bias).
-    ``state`` [slots, heads, d * dv] float32 is read and left updated, ``out`` [rows, heads * dv] float32
-    receives the sums.  ``max_q_len`` 1: every sequence brings one token, which has a kernel of its own."""
+    (``key_eps`` under the root).  ``decay`` and ``remove`` (float32 [rows, heads * d], row strides free) hold
+    pre-activations: w = exp(-decay_scale * sigmoid(decay + decay_bias)), a = sigmoid(remove + remove_bias); a
+    step of rows of more than one token overwrites both.  ``state`` [slots, heads, d * dv] float32 is read and
+    left updated, ``out`` [rows, heads * dv] float32 receives the sums.  ``max_q_len`` 1: every sequence brings
+    one token, which has a kernel of its own; it may be given ``low`` (float32 [rows, rank]) and ``w2``
+    ([heads * d, rank]) instead of ``decay`` and then forms the decay's pre-activation w2 tanh(low) itself."""
     _need(rkv, "delta_scan rows", dim=2, contiguous=False)
     _need(state, "state", torch.float32, 3)
     _need(out, "delta_scan out", torch.float32, 2)
@@ -1011,9 +1017,23 @@ def delta_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, heads: int
         raise KernelError(f"delta_scan: rows {tuple(rkv.shape)}, state {tuple(state.shape)}, out {tuple(out.shape)} for "
                           f"{heads} heads of {d} x {dv}")
     for t, nm in ((decay, "decay pre-activations"), (remove, "removal pre-activations")):
+        if t is None and nm.startswith("decay") and low is not None:
+            continue
+        if t is None:
+            raise KernelError(f"delta_scan: no {nm}")
         _need(t, nm, torch.float32, 2, contiguous=False)
         if t.shape != (rows, heads * d) or t.stride(1) != 1:
             raise KernelError(f"delta_scan: {nm} {tuple(t.shape)} for {heads} heads of {d}")
+    rank, w2_code = 0, F32
+    if low is not None:
+        _need(low, "decay projection", torch.float32, 2, contiguous=False)
+        if w2 is None:
+            raise KernelError("delta_scan: the decay's first product without its second matrix")
+        _need(w2, "decay matrix", dim=2)
+        rank = w2.shape[1]
+        if max_q_len != 1 or low.shape != (rows, rank) or low.stride(1) != 1 or w2.shape[0] != heads * d or rank > DELTA_FUSED_MAX_RANK:
+            raise KernelError(f"delta_scan: low {tuple(low.shape)}, w2 {tuple(w2.shape)} for rows of up to {max_q_len}")
+        w2_code = _code(w2.dtype)
     for t, nm in ((decay_bias, "decay bias"), (remove_bias, "removal bias")):
         if t is not None:
             _need(t, nm, torch.float32, 1)
@@ -1023,21 +1043,24 @@ def delta_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, heads: int
         _need(t, nm, torch.int32, 1)
         if t.numel() < nseq:
             raise KernelError(f"delta_scan: {nm} has {t.numel()} entries for {nseq} sequences")
-    unit = torch.empty((rows, heads * d), dtype=torch.float32, device=rkv.device)
-    dots = torch.empty((rows, heads, 2), dtype=torch.float32, device=rkv.device)
-    p = _DeltaStateParams(rkv.data_ptr(), rkv.stride(0), r_off, k_off, v_off, decay.data_ptr(), decay.stride(0),
-                          0 if decay_bias is None else decay_bias.data_ptr(), decay_scale, remove.data_ptr(), remove.stride(0),
-                          0 if remove_bias is None else remove_bias.data_ptr(), unit.data_ptr(), unit.stride(0), key_eps,
-                          dots.data_ptr(), state.data_ptr(), state.stride(0), state.stride(1), out.data_ptr(), out.stride(0),
-                          seq_slot.data_ptr(), seq_q_start.data_ptr(), seq_q_len.data_ptr(), rows, nseq, heads, d, dv,
-                          state.shape[0], int(max_q_len))
-    _check(_lib.gb_delta_scan(byref(p), _code(rkv.dtype), _stream()), 2)
+    single = int(max_q_len) == 1
+    dots = None if single else torch.empty((rows, heads, 4), dtype=torch.float32, device=rkv.device)
+    p = _DeltaStateParams(rkv.data_ptr(), rkv.stride(0), r_off, k_off, v_off, 0 if decay is None else decay.data_ptr(),
+                          0 if decay is None else decay.stride(0), 0 if decay_bias is None else decay_bias.data_ptr(), decay_scale,
+                          remove.data_ptr(), remove.stride(0), 0 if remove_bias is None else remove_bias.data_ptr(),
+                          0 if low is None else low.data_ptr(), 0 if low is None else low.stride(0), 0 if w2 is None else w2.data_ptr(), rank,
+                          key_eps, 0 if dots is None else dots.data_ptr(), state.data_ptr(), state.stride(0), state.stride(1),
+                          out.data_ptr(), out.stride(0), seq_slot.data_ptr(), seq_q_start.data_ptr(), seq_q_len.data_ptr(), rows, nseq,
+                          heads, d, dv, state.shape[0], int(max_q_len))
+    _check(_lib.gb_delta_scan(byref(p), _code(rkv.dtype), c_int(w2_code), _stream()), 1 if single else 2)
 
 
 def tanh_(z: torch.Tensor) -> None:
-    """In place: z = tanh(z), float32."""
-    _need(z, "tanh rows", torch.float32)
-    _check(_lib.gb_tanh(_ptr(z), c_int64(z.numel()), _stream()))
+    """In place: z = tanh(z), float32 [rows, cols] (the row stride is free)."""
+    _need(z, "tanh rows", torch.float32, 2, contiguous=False)
+    if z.stride(1) != 1:
+        raise KernelError("tanh: rows are not contiguous")
+    _check(_lib.gb_tanh(_ptr(z), c_int(z.shape[0]), c_int(z.shape[1]), c_int64(z.stride(0)), _stream()))
 
 
 # ---- attention with sigmoid weights and a short convolution ahead of it -----------------------
@@ -1048,7 +1071,7 @@ class _ConvQkvParams(Structure):
         ("q_out", c_void_p), ("q_out_stride", c_int64), ("row_pos", c_void_p), ("row_seq", c_void_p), ("seq_slot", c_void_p),
         ("seq_q_start", c_void_p), ("seq_q_len", c_void_p), ("block_table", c_void_p), ("bt_stride", c_int),
         ("k_plane", c_void_p), ("v_plane", c_void_p), ("rows", c_int), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int),
-        ("d", c_int), ("dv", c_int), ("pages", c_int), ("max_slots", c_int),
+        ("d", c_int), ("dv", c_int), ("pages", c_int), ("max_slots", c_int), ("max_q_len", c_int),
     ]
 
 
@@ -1090,8 +1113,8 @@ def conv_qkv(qkv: torch.Tensor, q_out: torch.Tensor, heads: int, kv_heads: int, 
                        q_out.data_ptr(), q_out.stride(0), batch.row_pos.data_ptr(), batch.row_seq.data_ptr(),
                        batch.seq_slot.data_ptr(), batch.seq_q_start.data_ptr(), batch.seq_q_len.data_ptr(),
                        block_table.data_ptr(), block_table.stride(0), k_plane.data_ptr(), v_plane.data_ptr(), rows, batch.nseq,
-                       heads, kv_heads, head_dim, value_dim, k_plane.shape[0], block_table.shape[0])
-    _check(_lib.gb_conv_qkv(byref(p), _code(qkv.dtype), _stream()), 2 if taps > 1 else 1)
+                       heads, kv_heads, head_dim, value_dim, k_plane.shape[0], block_table.shape[0], int(getattr(batch, "max_q_len", 0)))
+    _check(_lib.gb_conv_qkv(byref(p), _code(qkv.dtype), _stream()), 2 if taps > 1 and getattr(batch, "max_q_len", 0) != 1 else 1)
 
 
 class _SigmoidAttnParams(Structure):
@@ -1101,11 +1124,15 @@ class _SigmoidAttnParams(Structure):
 def attention_sigmoid(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, block_table: torch.Tensor,
                       batch, heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
                       value_dim: Optional[int] = None, score_bias: Optional[torch.Tensor] = None,
-                      gate: Optional[torch.Tensor] = None) -> None:
+                      gate: Optional[torch.Tensor] = None, algo: str = "auto") -> None:
     """Causal grouped-query attention over the paged cache with weights sigmoid((q . k) * scale + score_bias[h])
     that are not normalised over the keys; ``window`` > 0: row i sees keys j with 0 <= i - j < window.  With
     ``gate`` ([rows, heads] pre-activations, a view with a free row stride) head h's output is multiplied by
-    sigmoid(gate[row, h]).  out is [rows, heads * value_dim]."""
+    sigmoid(gate[row, h]).  out is [rows, heads * value_dim].  bfloat16 rows with key heads of 32, 64, 96 or
+    128 and value heads of 32, 48, 64 or 128 run on the tensor cores, everything else (and ``algo`` "simt")
+    on the CUDA cores."""
+    if algo not in ("auto", "simt"):
+        raise KernelError(f"attention_sigmoid: unknown algorithm '{algo}'")
     a = _attn_params(q, out, k_plane, v_plane, block_table, batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len,
                      batch.nseq, batch.max_q_len, heads, kv_heads, head_dim, scale, window, 1, None, value_dim)
     if score_bias is not None:
@@ -1124,6 +1151,8 @@ def attention_sigmoid(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor,
     p.score_bias = 0 if score_bias is None else score_bias.data_ptr()
     p.gate = 0 if gate is None else gate.data_ptr()
     p.gate_stride = gstride
+    if algo == "simt":
+        p.num_splits = -1
     _check(_lib.gb_attention_sigmoid(byref(p), _code(q.dtype), _stream()))
 
 
@@ -1187,3 +1216,67 @@ def moe_rows(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, index: torch
     p = _MoeRowsParams(x.data_ptr(), x.stride(0), up.data_ptr(), down.data_ptr(), act.data_ptr(), out.data_ptr(), out.stride(0),
                        index.data_ptr(), weight.data_ptr(), rows, experts, top, ff, hidden)
     _check(_lib.gb_moe_rows(byref(p), _code(x.dtype), _code(up.dtype), _stream()), 2)
+
+
+def moe_group(index: torch.Tensor, experts: int, offsets: torch.Tensor, place: torch.Tensor, src_row: torch.Tensor) -> None:
+    """Sort the (row, choice) pairs of ``index`` (int32 [rows, top]) by expert: ``offsets`` (int32 [experts + 1]) receives
+    where each expert's group starts, ``place`` (int32 [rows * top]) each pair's position in the sorted order and
+    ``src_row`` (int32 [rows * top]) the row of the pair at each position."""
+    _need(index, "chosen experts", torch.int32, 2)
+    rows, top = index.shape
+    for t, nm, n in ((offsets, "offsets", experts + 1), (place, "places", rows * top), (src_row, "source rows", rows * top)):
+        _need(t, nm, torch.int32, 1)
+        if t.numel() < n:
+            raise KernelError(f"moe_group: {nm} has {t.numel()} entries, want {n}")
+    _check(_lib.gb_moe_group(_ptr(index), c_int(rows), c_int(top), c_int(experts), _ptr(offsets), _ptr(place), _ptr(src_row), _stream()))
+
+
+def moe_gather(x: torch.Tensor, src_row: torch.Tensor, xs: torch.Tensor) -> None:
+    """xs[p] = x[src_row[p]]."""
+    _need(x, "moe x", dim=2, contiguous=False)
+    _need(xs, "gathered rows", x.dtype, 2)
+    _need(src_row, "source rows", torch.int32, 1)
+    if xs.shape[1] != x.shape[1] or src_row.numel() < xs.shape[0] or x.stride(1) != 1:
+        raise KernelError(f"moe_gather: x {tuple(x.shape)}, gathered {tuple(xs.shape)}, {src_row.numel()} source rows")
+    _check(_lib.gb_moe_gather(_ptr(x), c_int64(x.stride(0)), _ptr(src_row), _ptr(xs), c_int(xs.shape[0]), c_int(x.shape[1]), _code(x.dtype), _stream()))
+
+
+def relu2(z: torch.Tensor) -> None:
+    """In place: z = max(z, 0)^2."""
+    _need(z, "relu2 rows")
+    _check(_lib.gb_relu2(_ptr(z), c_int64(z.numel()), _code(z.dtype), _stream()))
+
+
+def moe_combine(ys: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = sum_k weight[r, k] * ys[place[r * top + k]], float32, in the order of k."""
+    _need(ys, "expert outputs", torch.float32, 2)
+    _need(place, "places", torch.int32, 1)
+    _need(weight, "chosen weights", torch.float32, 2)
+    _need(out, "moe out", torch.float32, 2, contiguous=False)
+    rows, top = weight.shape
+    if out.shape != (rows, ys.shape[1]) or ys.shape[0] != rows * top or place.numel() < rows * top or out.stride(1) != 1:
+        raise KernelError(f"moe_combine: outputs {tuple(ys.shape)}, weights {tuple(weight.shape)}, out {tuple(out.shape)}")
+    _check(_lib.gb_moe_combine(_ptr(ys), _ptr(place), _ptr(weight), _ptr(out), c_int64(out.stride(0)), c_int(rows), c_int(top), c_int(ys.shape[1]),
+                               _stream()))
+
+
+def gemm_w_cols(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> str:
+    """out = a @ w^T where ``w`` may be a block of columns of a wider matrix (its rows lie ``w.stride(0)`` apart): the
+    tiled tcgen05 kernels for aligned bfloat16 operands, else the CUDA-core kernel.  Returns the kernel's name."""
+    _need(a, "gemm a", dim=2, contiguous=False)
+    _need(w, "gemm w", dim=2, contiguous=False)
+    _need(out, "gemm out", dim=2, contiguous=False)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    fits = (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and out.dtype in (torch.float32, torch.bfloat16))
+    if not fits:
+        _check(_lib.gb_gemm_simt(_ptr(a), _code(a.dtype), _ptr(w), _code(w.dtype), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                 c_int64(a.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)), _stream()))
+        return "simt"
+    pair = M >= TC5_PAIR_MIN_ROWS
+    _check(_lib.gb_gemm_tc5_ldw(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K), c_int64(a.stride(0)),
+                                c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(1 if pair else 0), _stream()))
+    return "tc5_pair" if pair else "tc5"

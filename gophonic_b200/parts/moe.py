@@ -5,8 +5,12 @@ The router's logits are a float32 product and its softmax, choice and weights ar
 (``ops.moe_route``).  The experts' matrices are kept stacked: all up matrices one above the other and all
 down matrices side by side.  A step of many rows runs two products over the stack, with the row's weight
 for each expert (zero where it was not chosen) folded into the activation between them, so the experts a
-token did not choose contribute exact zeros and nothing depends on where the rows of an expert lie.  A
-step of few rows reads only the chosen experts' matrices (``ops.moe_rows``).
+token did not choose contribute exact zeros and nothing depends on where the rows of an expert lie; such
+a step stays free of host reads, so single-token steps of many sequences replay from a graph.  A step of
+few rows reads only the chosen experts' matrices (``ops.moe_rows``).  A prompt-sized step, which is never
+replayed from a graph, sorts its (row, choice) pairs by expert, reads the experts' group sizes on the host
+and runs one pair of products an expert on that expert's rows alone, so it does top / experts of the stacked
+path's arithmetic.
 """
 from __future__ import annotations
 
@@ -20,6 +24,7 @@ from .base import FeedForward, Runtime, TensorDecl
 class MoE(FeedForward):
     capturable = True
     ROWS_SPARSE = 16      # up to this many rows a step reads only the chosen experts' matrices
+    ROWS_GROUPED = 192    # from this many rows on a step runs every expert on its own rows (it reads their counts on the host)
 
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
@@ -57,7 +62,34 @@ class MoE(FeedForward):
         if rows <= self.ROWS_SPARSE and s.top < s.experts:
             ops.moe_rows(x, self.up, self.down, index, weight, out, s.experts, s.intermediate)
             return
+        if rows >= self.ROWS_GROUPED and s.top < s.experts and not torch.cuda.is_current_stream_capturing():
+            self._grouped(x, index, weight, out)
+            return
         act = torch.empty((rows, s.experts * s.intermediate), dtype=x.dtype, device=x.device)
         ops.gemm(x, self.up, act)
         ops.moe_act(act, dense, act, s.experts, s.intermediate)
         ops.gemm(act, self.down, out)
+
+    def _grouped(self, x: torch.Tensor, index: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+        """Every expert on its own rows: sort the pairs by expert, gather, two products an expert, add up."""
+        ops, s = self.rt.ops, self.spec
+        rows, pairs, ff = x.shape[0], x.shape[0] * s.top, s.intermediate
+        offsets = torch.empty(s.experts + 1, dtype=torch.int32, device=x.device)
+        place = torch.empty(pairs, dtype=torch.int32, device=x.device)
+        src_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
+        ops.moe_group(index, s.experts, offsets, place, src_row)
+        bounds = offsets.tolist()               # the one host read of a prompt-sized step
+        xs = torch.empty((pairs, s.hidden), dtype=x.dtype, device=x.device)
+        ops.moe_gather(x, src_row, xs)
+        act = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+        for e in range(s.experts):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                ops.gemm_w_cols(xs[lo:hi], self.up[e * ff:(e + 1) * ff], act[lo:hi])
+        ops.relu2(act)
+        ys = torch.empty((pairs, s.hidden), dtype=torch.float32, device=x.device)
+        for e in range(s.experts):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi > lo:
+                ops.gemm_w_cols(act[lo:hi], self.down[:, e * ff:(e + 1) * ff], ys[lo:hi])
+        ops.moe_combine(ys, place, weight, out)

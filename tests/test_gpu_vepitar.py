@@ -53,6 +53,11 @@ CONFIGS = {
     # heads of 128 and 256 key channels, one kv head for all heads, a convolution of two taps
     "wide": config([delta(heads=1, dim=128), attention(heads=4, kv_heads=1, dim=128, vdim=128, size=70, conv=2, scale=0.09, mlp=dense(64)),
                     delta(heads=1, dim=256, mlp=moe(8, 3, 16))], width=128, vocab=70, streams=4),
+    # key and value heads the tensor-core attention kernel takes in bfloat16, of unequal sizes, windows around a page
+    "tensor": config([attention(heads=4, kv_heads=2, dim=32, vdim=48, size=40, conv=4, mlp=moe(4, 2, 32)), delta(heads=2, dim=32),
+                      attention(heads=6, kv_heads=2, dim=64, vdim=64, size=100, conv=2, scale=0.1, mlp=dense(64)),
+                      attention(heads=2, kv_heads=1, dim=96, vdim=32, size=64, conv=3, scale=0.1),
+                      attention(heads=2, kv_heads=1, dim=128, vdim=128, size=7, conv=4, scale=0.09)], width=96, vocab=80),
     # no streams at all (the plain residual with its factor), one stream with coefficients, a factor of 1
     "plain": config([delta(mlp=dense(40)), attention(mlp=moe(4, 2, 24))], streams=None, mult=0.7),
     "one": config([attention(mlp=dense(40)), delta(mlp=moe(4, 2, 24))], streams=1, mult=1.0),
@@ -173,7 +178,7 @@ def test_token_by_token_equals_the_whole_prompt(models, name, graphs):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mix", "wide", "odd"])
+@pytest.mark.parametrize("name", ["mix", "wide", "odd", "tensor"])
 @pytest.mark.parametrize("cuts", [[2] * 40, [3, 64, 1, 2, 61], [63, 1, 1, 64], [130, 2]])
 def test_portions_of_a_prompt(models, cuts, dtype, name):
     cfg, w, _ = models[name]
@@ -234,7 +239,7 @@ def test_slots_and_pages_that_are_used_again(models):
     close(got, P.forward(cfg, w, b[:20]), TOL["float32"])
 
 
-@pytest.mark.parametrize("name", ["mix", "wide"])
+@pytest.mark.parametrize("name", ["mix", "wide", "tensor"])
 def test_long_decoding_past_windows_and_pages(models, name):
     cfg, w, _ = models[name]
     toks = tokens_for(cfg, 5, 40 + 230)
@@ -284,9 +289,10 @@ def _attention_case(rng, T, heads, kv_heads, d, dv, window):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("algo", ["auto", "simt"])
 @pytest.mark.parametrize("shape", [(2, 1, 16, 8, 37), (4, 4, 24, 24, 70), (3, 1, 8, 40, 64), (4, 2, 32, 32, 65), (2, 1, 64, 64, 1),
-                                   (3, 3, 128, 128, 130), (2, 2, 16, 16, 0)])
-def test_attention_kernel_at_the_edges(shape, dtype):
+                                   (3, 3, 128, 128, 130), (2, 2, 16, 16, 0), (4, 1, 96, 32, 40), (2, 2, 64, 48, 200), (2, 1, 32, 128, 0)])
+def test_attention_kernel_at_the_edges(shape, dtype, algo):
     import torch
     from types import SimpleNamespace
     from gophonic_b200 import ops
@@ -322,7 +328,7 @@ def test_attention_kernel_at_the_edges(shape, dtype):
         out = torch.zeros((rows, heads * dv), dtype=td, device=dev)
         batch = SimpleNamespace(seq_slot=i32(1), seq_q_start=i32(0), seq_q_len=i32(rows), seq_kv_len=i32(kv_len), nseq=1, max_q_len=rows)
         ops.attention_sigmoid(qq, out, k_plane, v_plane, table, batch, heads, kv_heads, d, scale, window, value_dim=dv, score_bias=bt,
-                              gate=gt[first:first + rows])
+                              gate=gt[first:first + rows], algo=algo)
         return out.float().cpu().numpy().reshape(rows, heads, dv)
     close(run(T, 0, T), want, tol)                                   # the whole prompt
     close(run(T - 200, 200, T), want[200:], tol)                     # a portion that continues a cached prefix
@@ -364,8 +370,9 @@ def test_convolution_norm_and_cache_write(shape, dtype):
     i32 = lambda a: torch.tensor(a, dtype=torch.int32, device=dev)
     tol = 2e-5 if dtype == "float32" else 2e-2
     at = [0, 0, 0]
-    # the three sequences advance together in portions of unequal sizes, down to one and two tokens
-    for sizes in ([64, 1, 30], [1, 2, 1], [2, 0, 39], [83, 0, 0]):
+    # the three sequences advance together in portions of unequal sizes, then by single tokens (whose kernel moves the
+    # state on itself), then in portions again
+    for sizes in ([62, 1, 30], [2, 1, 0], [1, 1, 1], [1, 0, 1], [84, 0, 38]):
         live = [i for i in range(3) if sizes[i] > 0]
         rows = sum(sizes)
         qkv = torch.cat([seqs[i][0][at[i]:at[i] + sizes[i]] for i in live])
@@ -373,7 +380,7 @@ def test_convolution_norm_and_cache_write(shape, dtype):
         row_seq = np.concatenate([np.full(sizes[i], j) for j, i in enumerate(live)])
         starts = np.cumsum([0] + [sizes[i] for i in live])[:-1]
         batch = SimpleNamespace(row_pos=i32(row_pos), row_seq=i32(row_seq), seq_slot=i32([i + 1 for i in live]), seq_q_start=i32(starts),
-                                seq_q_len=i32([sizes[i] for i in live]), nseq=len(live))
+                                seq_q_len=i32([sizes[i] for i in live]), nseq=len(live), max_q_len=max(sizes))
         q_out = torch.empty((rows, qd), dtype=td, device=dev)
         ops.conv_qkv(qkv, q_out, heads, kv_heads, d, dv, conv_t, state if taps > 1 else None, True, True, eps, batch, table, k_plane, v_plane)
         got = q_out.float().cpu().numpy().reshape(rows, heads, d)
@@ -402,14 +409,18 @@ def test_delta_recurrence_kernel(shape, dtype):
     lengths = [45, 1, 19]
     scale_w, key_eps = 0.6, 1e-6
     width = 2 * heads * d + heads * dv
+    # the decay's pre-activation is itself a product, w2 tanh(low): steps of single tokens are given its factors
+    rank = 6
+    w2 = torch.tensor(rng.standard_normal((heads * d, rank)), dtype=torch.float32).to(td)
     seqs = []
     for n in lengths:
         rkv = torch.tensor(rng.standard_normal((n, width)), dtype=torch.float32).to(td)
-        zw, za = rng.standard_normal((n, heads * d)), 2.0 * rng.standard_normal((n, heads * d))
-        seqs.append((rkv, zw.astype(np.float32), za.astype(np.float32)))
+        low = rng.standard_normal((n, rank)).astype(np.float32)
+        zw, za = np.tanh(low.astype(np.float64)) @ w2.float().numpy().astype(np.float64).T, 2.0 * rng.standard_normal((n, heads * d))
+        seqs.append((rkv, zw.astype(np.float32), za.astype(np.float32), low))
     bw, ba = rng.standard_normal(heads * d).astype(np.float32), rng.standard_normal(heads * d).astype(np.float32)
     want = []
-    for rkv, zw, za in seqs:
+    for rkv, zw, za, _ in seqs:
         x = rkv.float().numpy().astype(np.float64)
         n = x.shape[0]
         r, k = x[:, :heads * d].reshape(n, heads, d), x[:, heads * d:2 * heads * d].reshape(n, heads, d)
@@ -430,8 +441,13 @@ def test_delta_recurrence_kernel(shape, dtype):
         rkv = torch.cat([seqs[i][0][at[i]:at[i] + sizes[i]] for i in live]).to(dev)
         starts = np.cumsum([0] + [sizes[i] for i in live])[:-1]
         out = torch.empty((rows, heads * dv), dtype=torch.float32, device=dev)
-        ops.delta_scan(rkv, 0, heads * d, 2 * heads * d, heads, d, dv, f32(cat(1)), f32(bw), scale_w, f32(cat(2)), f32(ba), key_eps, state, out,
-                       i32([i + 1 for i in live]), i32(starts), i32([sizes[i] for i in live]), len(live), max_q_len=max(sizes))
+        if max(sizes) == 1:
+            ops.delta_scan(rkv, 0, heads * d, 2 * heads * d, heads, d, dv, None, f32(bw), scale_w, f32(cat(2)), f32(ba), key_eps, state, out,
+                           i32([i + 1 for i in live]), i32(starts), i32([sizes[i] for i in live]), len(live), max_q_len=1,
+                           low=f32(cat(3)), w2=w2.to(dev))
+        else:
+            ops.delta_scan(rkv, 0, heads * d, 2 * heads * d, heads, d, dv, f32(cat(1)), f32(bw), scale_w, f32(cat(2)), f32(ba), key_eps, state, out,
+                           i32([i + 1 for i in live]), i32(starts), i32([sizes[i] for i in live]), len(live), max_q_len=max(sizes))
         got = out.cpu().numpy().reshape(rows, heads, dv)
         for j, i in enumerate(live):
             ref = want[i][0][at[i]:at[i] + sizes[i]]
@@ -496,7 +512,7 @@ def test_router_and_experts(shape):
     tensors = {n: torch.tensor(a, dtype=torch.float32, device=dev) for n, a in w.items()}
     w = {n: t.cpu().numpy().astype(np.float64) for n, t in tensors.items()}
     part = MoE(spec, "", tensors, Runtime(dev, torch.float32, ops))
-    for rows in (3, 50):                   # few rows read the chosen experts only, many run the stacked products
+    for rows in (3, 50, 300):              # few rows read the chosen experts only, more run the stacked products, many every expert on its own rows
         h = rng.standard_normal((rows, width)).astype(np.float32)
         out = torch.empty((rows, width), dtype=torch.float32, device=dev)
         part.forward(None, torch.tensor(h, device=dev), out)

@@ -175,8 +175,145 @@ __global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(SigmoidAttnParams
     }
 }
 
+// Single tokens: a CTA owns one (sequence, kv head); the 16 rows of its tiles are the query heads of the group,
+// so the group's heads share every key and value that is read.  The four warps take 16 keys each of every page
+// and keep sums of their own, which meet in shared memory at the end (the weights are not normalised: the sums
+// simply add).
+template <int HD, int DV>
+__global__ void __launch_bounds__(128) attn_sigmoid_decode_mma_kernel(SigmoidAttnParams p) {
+    constexpr int SD = HD + 8, SV = DV + 8, KS = HD / 16, NF = DV / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);      // [16][SD]
+    bf16* Ks = Qs + 16 * SD;                           // [2][64][SD]
+    bf16* Vs = Ks + 2 * 64 * SD;                       // [2][64][SV]
+    float* red = reinterpret_cast<float*>(Vs + 2 * 64 * SV);   // [4][16][DV + 1]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int seq = blockIdx.y, kvh = blockIdx.x;
+    const int G = p.heads / p.kv_heads;
+    const int pos = p.seq_kv_len[seq] - 1;             // the token's position
+    const int64_t row = p.seq_q_start[seq];
+    const int* bt = block_table_row(p.block_table, p.bt_stride, p.seq_slot[seq], p.max_slots);
+    const bf16* kbase = (const bf16*)p.k_plane;
+    const bf16* vbase = (const bf16*)p.v_plane;
+    {
+        constexpr int CH = HD / 8;
+        const bf16* qsrc = (const bf16*)p.q + row * p.q_row_stride + (int64_t)kvh * G * HD;
+        for (int idx = tid; idx < 16 * CH; idx += 128) {
+            int r = idx / CH, c = idx - r * CH;
+            bool ok = r < G;
+            cp_async16(Qs + r * SD + c * 8, ok ? qsrc + (int64_t)r * HD + c * 8 : qsrc, ok ? 16 : 0);
+        }
+    }
+    int lo_pos = 0;
+    if (p.window > 0) {
+        lo_pos = pos - p.window + 1;
+        if (lo_pos < 0) lo_pos = 0;
+    }
+    const int t_lo = lo_pos / 64, t_hi = pos / 64;
+    const int n_tiles = t_hi - t_lo + 1;
+    auto load_tile = [&](int t, int buf) {
+        int64_t page = page_of(bt, t * 64, p.bt_stride, p.pages);
+        int64_t at = (page * p.kv_heads + kvh) * 64;
+        load_page<HD>(Ks + buf * 64 * SD, kbase + at * HD, tid, 128);
+        load_page<DV>(Vs + buf * 64 * SV, vbase + at * DV, tid, 128);
+    };
+    load_tile(t_lo, 0);
+    cp_async_commit();
+
+    const float sc = p.scale * LOG2E;
+    const int h0 = kvh * G + g, h1 = h0 + 8;           // the heads of this thread's two rows
+    const float bias0 = (p.score_bias && g < G ? p.score_bias[h0] : 0.f) * LOG2E;
+    const float bias1 = (p.score_bias && g + 8 < G ? p.score_bias[h1] : 0.f) * LOG2E;
+    float o[NF][4];
+#pragma unroll
+    for (int j = 0; j < NF; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) o[j][e] = 0.f;
+    uint32_t qf[KS][4];
+    for (int ti = 0; ti < n_tiles; ti++) {
+        const int t = t_lo + ti;
+        const int buf = ti & 1;
+        cp_async_wait<0>();
+        __syncthreads();
+        if (ti + 1 < n_tiles) load_tile(t + 1, buf ^ 1);
+        cp_async_commit();
+        if (ti == 0) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) ldmatrix_x4(qf[ks], Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks * 16 + (lane >> 4) * 8);
+        }
+        const bf16* kt = Ks + buf * 64 * SD;
+        const bf16* vt = Vs + buf * 64 * SV;
+        float s[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) s[j][e] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            uint32_t b[4];
+            ldmatrix_x4(b, kt + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks * 16 + ((lane >> 3) & 1) * 8);
+            mma_bf16_16816(s[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b[0], b[1]);
+            mma_bf16_16816(s[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b[2], b[3]);
+        }
+        uint32_t pa[4];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            float w[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int key = t * 64 + warp * 16 + j * 8 + t4 * 2 + (e & 1);
+                const bool ok = key <= pos && (p.window <= 0 || key > pos - p.window);
+                w[e] = ok ? __fdividef(1.f, 1.f + exp2f(-fmaf(s[j][e], sc, (e & 2) ? bias1 : bias0))) : 0.f;
+            }
+            pa[j * 2] = pack_bf16(w[0], w[1]);
+            pa[j * 2 + 1] = pack_bf16(w[2], w[3]);
+        }
+#pragma unroll
+        for (int c = 0; c < DV / 16; c++) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, vt + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SV + c * 16 + (lane >> 4) * 8);
+            mma_bf16_16816(o[c * 2], pa[0], pa[1], pa[2], pa[3], b[0], b[1]);
+            mma_bf16_16816(o[c * 2 + 1], pa[0], pa[1], pa[2], pa[3], b[2], b[3]);
+        }
+    }
+    cp_async_wait<0>();
+    // the four warps' sums, in warp order
+#pragma unroll
+    for (int j = 0; j < NF; j++) {
+        float* r0 = red + ((warp * 16 + g) * (DV + 1)) + j * 8 + t4 * 2;
+        float* r1 = red + ((warp * 16 + g + 8) * (DV + 1)) + j * 8 + t4 * 2;
+        r0[0] = o[j][0], r0[1] = o[j][1], r1[0] = o[j][2], r1[1] = o[j][3];
+    }
+    __syncthreads();
+    const bf16* gate = (const bf16*)p.gate;
+    for (int idx = tid; idx < G * DV; idx += 128) {
+        const int r = idx / DV, c = idx - r * DV;
+        const int head = kvh * G + r;
+        float a = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) a += red[(w * 16 + r) * (DV + 1) + c];
+        if (gate) a *= 1.f / (1.f + expf(-__bfloat162float(gate[row * p.gate_stride + head])));
+        ((bf16*)p.out)[row * p.out_row_stride + (int64_t)head * DV + c] = __float2bfloat16_rn(a);
+    }
+}
+
 template <int HD, int DV>
 int launch_mma_dv(const SigmoidAttnParams& p, cudaStream_t stream) {
+    if (p.max_q_len == 1 && p.heads / p.kv_heads <= 16) {
+        const size_t dsmem = (size_t)(16 * (HD + 8) + 2 * 64 * (HD + 8) + 2 * 64 * (DV + 8)) * sizeof(bf16) + (size_t)4 * 16 * (DV + 1) * sizeof(float);
+        static bool dconfigured = false;
+        if (!dconfigured && dsmem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(attn_sigmoid_decode_mma_kernel<HD, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsmem);
+            if (e != cudaSuccess) GB_REFUSE("attention_sigmoid: cannot reserve %zu bytes of shared memory: %s", dsmem, cudaGetErrorString(e));
+            dconfigured = true;
+        }
+        dim3 dgrid(p.kv_heads, p.nseq);
+        if (dgrid.y > 65535) GB_REFUSE("attention_sigmoid: %d sequences exceed one launch", p.nseq);
+        attn_sigmoid_decode_mma_kernel<HD, DV><<<dgrid, 128, dsmem, stream>>>(p);
+        GB_CHECK_LAUNCH("attention_sigmoid_decode_mma");
+        return 0;
+    }
     const size_t smem = (size_t)(3 * 64 * (HD + 8) + 2 * 64 * (DV + 8)) * sizeof(bf16);
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {

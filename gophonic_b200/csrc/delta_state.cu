@@ -262,9 +262,11 @@ __global__ void __launch_bounds__(THREADS) delta_scan_kernel(DeltaStateParams p)
 // eight groups' partial sums meet in shared memory.  The CTA prepares the token itself (decay, removal
 // rate, the key's length, the two dot products: a thread a channel, sums over the CTA), and with `low` and
 // `w2` also the decay's pre-activation, z = W2 tanh(low), so that a step needs no kernel ahead of this one.
+// That pays for a few sequences; with many, the eight CTAs of a head would each repeat the preparation ahead
+// of their state arithmetic, and the preparation kernel runs first instead (PREPARED).
 constexpr int STEP_MAX_RANK = 256;
 
-template <typename T, typename TW, int R>
+template <typename T, typename TW, int R, bool PREPARED>
 __global__ void __launch_bounds__(THREADS) delta_step_kernel(DeltaStateParams p) {
     __shared__ float rw_s[SLICES * R], au_s[SLICES * R], k_s[SLICES * R], w_s[SLICES * R];
     __shared__ float red[2][SLICES][COLS + 1];
@@ -288,7 +290,19 @@ __global__ void __launch_bounds__(THREADS) delta_step_kernel(DeltaStateParams p)
     }
     const T* rp = (const T*)p.rkv + row * p.row_stride;
     const float vj = mine ? to_f32<T>(rp[p.v_off + h * dv + j]) : 0.f;
-    if (p.low) {
+    if (PREPARED) {
+        for (int c = tid; c < SLICES * R; c += THREADS) {
+            float rw = 0.f, au = 0.f, k = 0.f, w = 1.f;
+            if (c < d) {
+                w = p.decay[row * p.decay_stride + h * d + c];
+                au = p.remove[row * p.remove_stride + h * d + c];
+                k = to_f32<T>(rp[p.k_off + h * d + c]);
+                rw = to_f32<T>(rp[p.r_off + h * d + c]) * w;
+            }
+            rw_s[c] = rw, au_s[c] = au, k_s[c] = k, w_s[c] = w;
+        }
+    }
+    if (!PREPARED && p.low) {
         for (int i = tid; i < p.rank; i += THREADS) low_s[i] = tanhf(p.low[row * p.low_stride + i]);
         __syncthreads();
     }
@@ -298,7 +312,7 @@ __global__ void __launch_bounds__(THREADS) delta_step_kernel(DeltaStateParams p)
 #pragma unroll
     for (int e = 0; e < 2; e++) {
         const int c = tid + e * THREADS;
-        if (c < d && c < SLICES * R) {
+        if (!PREPARED && c < d && c < SLICES * R) {
             kv[e] = to_f32<T>(rp[p.k_off + h * d + c]);
             rv[e] = to_f32<T>(rp[p.r_off + h * d + c]);
             float z;
@@ -311,11 +325,16 @@ __global__ void __launch_bounds__(THREADS) delta_step_kernel(DeltaStateParams p)
             kk = fmaf(kv[e], kv[e], kk);
         }
     }
+    float inv, aur = 0.f, kr = 0.f;
+    if (PREPARED) {
+        const float4 t4 = *reinterpret_cast<const float4*>(p.dots + (row * p.heads + h) * 4);
+        aur = t4.x, kr = t4.y, inv = t4.z;
+        __syncthreads();
+    } else {
     kk = warp_sum(kk);
     if ((tid & 31) == 0) part[0][tid >> 5] = kk;
     __syncthreads();
-    const float inv = 1.0f / sqrtf(part[0][0] + part[0][1] + part[0][2] + part[0][3] + p.key_eps);
-    float aur = 0.f, kr = 0.f;
+    inv = 1.0f / sqrtf(part[0][0] + part[0][1] + part[0][2] + part[0][3] + p.key_eps);
 #pragma unroll
     for (int e = 0; e < 2; e++) {
         const int c = tid + e * THREADS;
@@ -332,6 +351,7 @@ __global__ void __launch_bounds__(THREADS) delta_step_kernel(DeltaStateParams p)
     __syncthreads();
     aur = part[1][0] + part[1][1] + part[1][2] + part[1][3];
     kr = part[2][0] + part[2][1] + part[2][2] + part[2][3];
+    }
     float p1 = 0.f, p2 = 0.f;
 #pragma unroll
     for (int i = 0; i < R; i++) {
@@ -373,14 +393,14 @@ int launch_rc(const DeltaStateParams& p, dim3 grid, cudaStream_t stream) {
     return 0;
 }
 
-template <typename T, typename TW>
+template <typename T, typename TW, bool PREPARED>
 int launch_step(const DeltaStateParams& p, dim3 grid, cudaStream_t stream) {
     if (p.d <= 64)
-        delta_step_kernel<T, TW, 8><<<grid, THREADS, 0, stream>>>(p);
+        delta_step_kernel<T, TW, 8, PREPARED><<<grid, THREADS, 0, stream>>>(p);
     else if (p.d <= 128)
-        delta_step_kernel<T, TW, 16><<<grid, THREADS, 0, stream>>>(p);
+        delta_step_kernel<T, TW, 16, PREPARED><<<grid, THREADS, 0, stream>>>(p);
     else
-        delta_step_kernel<T, TW, 32><<<grid, THREADS, 0, stream>>>(p);
+        delta_step_kernel<T, TW, 32, PREPARED><<<grid, THREADS, 0, stream>>>(p);
     GB_CHECK_LAUNCH("delta_step");
     return 0;
 }
@@ -389,14 +409,15 @@ template <typename T>
 int launch(const DeltaStateParams& p, int w2_dtype, cudaStream_t stream) {
     dim3 grid((p.dv + COLS - 1) / COLS, p.heads, p.nseq);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("delta_scan: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);
-    if (p.max_q_len == 1) {      // every sequence brings one token: one kernel does it all
-        if (p.low && w2_dtype == GB_BF16) return launch_step<T, __nv_bfloat16>(p, grid, stream);
-        return launch_step<T, float>(p, grid, stream);
+    if (p.max_q_len == 1 && (p.low || !p.dots)) {      // every sequence brings one token and nothing is prepared: one kernel does it all
+        if (p.low && w2_dtype == GB_BF16) return launch_step<T, __nv_bfloat16, false>(p, grid, stream);
+        return launch_step<T, float, false>(p, grid, stream);
     }
     dim3 pgrid(p.rows, (p.heads + 3) / 4);
     if (pgrid.y > 65535) GB_REFUSE("delta_scan: %d heads exceed one launch", p.heads);
     delta_prep_kernel<T><<<pgrid, 128, 0, stream>>>(p);
     GB_CHECK_LAUNCH("delta_prep");
+    if (p.max_q_len == 1) return launch_step<T, float, true>(p, grid, stream);
     const int rc = ((p.d + SLICES - 1) / SLICES + 3) / 4 * 4;
     switch (rc) {
         case 4: return launch_rc<T, 4>(p, grid, stream);

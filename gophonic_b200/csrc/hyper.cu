@@ -17,14 +17,14 @@
 
 namespace {
 
-constexpr int HC_THREADS = 256;
+constexpr int HC_MAX_THREADS = 1024;
 
 template <typename TO, int S>
-__global__ void __launch_bounds__(HC_THREADS) hyper_mix_norm_kernel(HyperParams p) {
+__global__ void __launch_bounds__(HC_MAX_THREADS) hyper_mix_norm_kernel(HyperParams p) {
     extern __shared__ float u_s[];          // the row's u, [width]
-    __shared__ float red[HC_THREADS / 32];
+    __shared__ float red[HC_MAX_THREADS / 32];
     __shared__ float coef[S * S + 2 * S];   // mix, out, in
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, HC_THREADS = blockDim.x;
     const int64_t r = p.row_index ? p.row_index[blockIdx.x] : (int64_t)blockIdx.x;
     const bool write = p.y != nullptr, store = write && !p.row_index;
     for (int i = tid; i < S * S + 2 * S; i += HC_THREADS) {
@@ -77,7 +77,6 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_mix_norm_kernel(HyperParams 
     if ((tid & 31) == 0) red[tid >> 5] = ss;
     __syncthreads();
     float total = 0.f;
-#pragma unroll
     for (int i = 0; i < HC_THREADS / 32; i++) total += red[i];
     const float inv = 1.0f / sqrtf(total / (float)p.width + p.eps);
     TO* o = (TO*)p.x_out + (int64_t)blockIdx.x * p.width;
@@ -92,7 +91,10 @@ int launch_s(const HyperParams& p, cudaStream_t stream) {
         cudaError_t e = cudaFuncSetAttribute(hyper_mix_norm_kernel<TO, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) GB_REFUSE("hyper_mix_norm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
-    hyper_mix_norm_kernel<TO, S><<<p.rows, HC_THREADS, smem, stream>>>(p);
+    // few rows: more threads a row, so that enough loads are in flight
+    int threads = p.rows >= 1024 ? 256 : (p.rows >= 256 ? 512 : 1024);
+    while (threads > 64 && threads > p.width) threads >>= 1;
+    hyper_mix_norm_kernel<TO, S><<<p.rows, threads, smem, stream>>>(p);
     GB_CHECK_LAUNCH("hyper_mix_norm");
     return 0;
 }

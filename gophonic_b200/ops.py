@@ -999,7 +999,7 @@ def delta_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, heads: int
                decay_bias: Optional[torch.Tensor], decay_scale: float, remove: torch.Tensor, remove_bias: Optional[torch.Tensor],
                key_eps: float, state: torch.Tensor, out: torch.Tensor, seq_slot: torch.Tensor, seq_q_start: torch.Tensor,
                seq_q_len: torch.Tensor, nseq: int, max_q_len: int = 0, low: Optional[torch.Tensor] = None,
-               w2: Optional[torch.Tensor] = None) -> None:
+               w2: Optional[torch.Tensor] = None, prepare: bool = False) -> None:
     """The generalized delta rule over the rows of a step, token by token, for every (sequence, head):
     S <- diag(w) S - (a u)(u^T S) + k v^T from the old S, o = S^T r, with u the key over its length
     (``key_eps`` under the root).  ``decay`` and ``remove`` (float32 [rows, heads * d], row strides free) hold
@@ -1007,7 +1007,9 @@ def delta_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, heads: int
     step of rows of more than one token overwrites both.  ``state`` [slots, heads, d * dv] float32 is read and
     left updated, ``out`` [rows, heads * dv] float32 receives the sums.  ``max_q_len`` 1: every sequence brings
     one token, which has a kernel of its own; it may be given ``low`` (float32 [rows, rank]) and ``w2``
-    ([heads * d, rank]) instead of ``decay`` and then forms the decay's pre-activation w2 tanh(low) itself."""
+    ([heads * d, rank]) instead of ``decay`` and then forms the decay's pre-activation w2 tanh(low) and
+    everything else of the token itself, in one kernel.  ``prepare`` asks a single-token step with ``decay`` for
+    the preparation kernel ahead of a lean recurrence kernel (worth it from a few dozen sequences on)."""
     _need(rkv, "delta_scan rows", dim=2, contiguous=False)
     _need(state, "state", torch.float32, 3)
     _need(out, "delta_scan out", torch.float32, 2)
@@ -1043,7 +1045,7 @@ def delta_scan(rkv: torch.Tensor, r_off: int, k_off: int, v_off: int, heads: int
         _need(t, nm, torch.int32, 1)
         if t.numel() < nseq:
             raise KernelError(f"delta_scan: {nm} has {t.numel()} entries for {nseq} sequences")
-    single = int(max_q_len) == 1
+    single = int(max_q_len) == 1 and not (prepare and low is None)
     dots = None if single else torch.empty((rows, heads, 4), dtype=torch.float32, device=rkv.device)
     p = _DeltaStateParams(rkv.data_ptr(), rkv.stride(0), r_off, k_off, v_off, 0 if decay is None else decay.data_ptr(),
                           0 if decay is None else decay.stride(0), 0 if decay_bias is None else decay_bias.data_ptr(), decay_scale,

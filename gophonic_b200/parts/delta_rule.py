@@ -21,6 +21,7 @@ from .linear_state import _StateMixer
 
 class DeltaRule(_StateMixer):
     NAMES = ("r", "k", "v", "g")
+    FUSED_ROWS = 16
 
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
@@ -68,14 +69,17 @@ class DeltaRule(_StateMixer):
         remove, low = both[:, :self.kd], both[:, self.kd:]
         o = torch.empty((rows, self.vd), dtype=torch.float32, device=x.device)
         decay = None
-        fused = batch.max_q_len == 1 and self.rank <= ops.DELTA_FUSED_MAX_RANK
+        # few single tokens: one kernel from the projections to the sums; many: the preparation kernel runs once a
+        # (token, head) instead of once a CTA
+        fused = batch.max_q_len == 1 and rows <= self.FUSED_ROWS and self.rank <= ops.DELTA_FUSED_MAX_RANK
         if not fused:
             ops.tanh_(low)
             decay = torch.empty((rows, self.kd), dtype=torch.float32, device=x.device)
             ops.gemm(low, self.w2, decay)
         ops.delta_scan(buf, 0, self.kd, 2 * self.kd, s.heads, s.key_dim, s.value_dim, decay, self.w_bias, float(s.decay_scale),
                        remove, self.a_bias, float(s.key_eps), cache.state, o, batch.seq_slot, batch.seq_q_start, batch.seq_q_len,
-                       batch.nseq, max_q_len=batch.max_q_len, low=low if fused else None, w2=self.w2 if fused else None)
+                       batch.nseq, max_q_len=batch.max_q_len, low=low if fused else None, w2=self.w2 if fused else None,
+                       prepare=not fused)
         y = torch.empty((rows, self.vd), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(o, buf[:, self.g_off:self.g_off + self.vd], y, s.heads, s.value_dim, ops.GATE_SIGMOID,
                            weight=self.norm_w, eps=float(s.eps))

@@ -507,6 +507,71 @@ def probe(name, **opts):
             work, unit = 2.0 * n_pages * kvh * 64 * d * 2, "GB/s"
         else:
             work, unit = 2.0 * heads * d * q_len * q_len, "TFLOP/s"
+    elif name in ("delta_scan_prompt", "state_scan_prompt", "delta_step_b64", "state_step_b64"):
+        # the recurrences of the matrix-state mixers by themselves, 16 heads of 128 x 128: one prompt of 2048 tokens
+        # (bound by each token's chain of dependent sums), or one token for each of 64 sequences (bound by reading
+        # and writing the states once: 134 MB)
+        heads, d = 16, 128
+        prompt = name.endswith("prompt")
+        nseq, q_len = (1, 2048) if prompt else (64, 1)
+        rows = nseq * q_len
+        f32 = lambda *shape: torch.randn(*shape, device=dev, generator=g)
+        rkv = rnd(rows, 3 * heads * d, scale=0.5)
+        state = torch.zeros((nseq, heads, d * d), dtype=torch.float32, device=dev)
+        out = torch.empty((rows, heads * d), dtype=torch.float32, device=dev)
+        ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        slot, start, ql = ints(list(range(nseq))), ints([i * q_len for i in range(nseq)]), ints([q_len] * nseq)
+        if name.startswith("delta"):
+            zw, za, bias = f32(rows, heads * d), f32(rows, heads * d), f32(heads * d)
+
+            def fn():
+                ops.delta_scan(rkv, 0, heads * d, 2 * heads * d, heads, d, d, zw.clone(), bias, 0.6, za.clone(), bias, 1e-6, state, out, slot, start,
+                               ql, nseq, max_q_len=q_len, prepare=True)
+        else:
+            decay = torch.sigmoid(f32(rows, heads * d) + 3.0)
+
+            def fn():
+                ops.state_scan(rkv, 0, heads * d, 2 * heads * d, heads, d, d, d ** -0.5, state, out, slot, start, ql, nseq, decay=decay,
+                               max_q_len=q_len)
+        if prompt:
+            work, unit = float(rows) * heads * d * d, "state updates/s"
+        else:
+            work, unit = 2.0 * state.numel() * 4, "GB/s"
+    elif name in ("attn_sigmoid_prefill", "attn_window_prefill", "attn_sigmoid_decode_b64", "attn_window_decode_b64"):
+        # windowed attention of 16 heads over 8 kv heads of 128, window 1024: with sigmoid weights, and with the softmax,
+        # kept first tokens and sink of the other design; a prompt of 2048 tokens, or one token for each of 64 sequences
+        heads, kvh, d, window = 16, 8, 128, 1024
+        prompt = name.endswith("prefill")
+        nseq, q_len, kv_len = (1, 2048, 2048) if prompt else (64, 1, 2048)
+        pages_per = (kv_len + 63) // 64
+        n_pages = nseq * pages_per
+        k, v = rnd(n_pages, kvh, 64, d), rnd(n_pages, kvh, 64, d)
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(nseq, pages_per)
+        q = rnd(nseq * q_len, heads * d)
+        out = torch.empty_like(q)
+        ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        slot, start = ints(list(range(nseq))), ints([i * q_len for i in range(nseq)])
+        ql, kl = ints([q_len] * nseq), ints([kv_len] * nseq)
+        if "sigmoid" in name:
+            from types import SimpleNamespace
+            rows_of = SimpleNamespace(seq_slot=slot, seq_q_start=start, seq_q_len=ql, seq_kv_len=kl, nseq=nseq, max_q_len=q_len)
+            bias, gate = torch.randn(heads, device=dev, generator=g) - 4.0, rnd(nseq * q_len, heads)
+
+            def fn():
+                ops.attention_sigmoid(q, out, k, v, table, rows_of, heads, kvh, d, d ** -0.5, window, score_bias=bias, gate=gate)
+        else:
+            from gophonic_b200.parts.attention import choose_splits
+            splits = 1 if q_len > 1 else choose_splits(nseq * kvh, window + 4)
+            scratch = torch.empty(ops.attention_scratch_floats(nseq, heads, d, splits), dtype=torch.float32, device=dev) if splits > 1 else None
+
+            def fn():
+                ops.attention(q, out, k, v, table, slot, start, ql, kl, nseq, q_len, heads, kvh, d, d ** -0.5, window, splits, scratch,
+                              keep_first=4, sink=True)
+        if prompt:
+            seen = sum(min(i + 1, window) for i in range(q_len))
+            work, unit = 4.0 * heads * d * seen, "TFLOP/s"
+        else:
+            work, unit = 2.0 * nseq * kvh * (window + 64) * d * 2, "GB/s"
     elif name in ("prefill_step", "decode_step"):
         # a whole engine step of a 4-layer model with the layer sizes of the benchmark (or of --model):
         # the launch list of a profiler then shows every kernel of a layer with its share.  --batch

@@ -25,8 +25,8 @@
 
 namespace {
 
-constexpr int COLS = 16;     // value columns per CTA
-constexpr int SLICES = 8;    // slices of the key channels
+constexpr int COLS = 16;     // value columns per CTA of the single-token kernel
+constexpr int SLICES = 8;    // its slices of the key channels
 constexpr int TT = 8;        // tokens staged at a time
 constexpr int THREADS = 128;
 
@@ -104,13 +104,18 @@ __global__ void __launch_bounds__(128) delta_prep_kernel(DeltaStateParams p) {
 }
 
 // ------------------------------------------------------------------------------------------
-// the scan.  RC: key channels per slice (a multiple of 4, RC * 8 >= d).  A warp owns 4 columns and its
-// 8 groups of lanes a slice of the key channels each; a thread keeps its RC state elements in registers
-// across all tokens of the step.  A tile's rows are fetched into registers while the tile before it is
+// the scan.  SLICES: slices of the key channels (8 or 16); RC: key channels per slice (a multiple of 4,
+// RC * SLICES >= d).  A warp owns 32 / SLICES columns and its groups of lanes a slice of the key channels each; a
+// thread keeps its RC state elements in registers across all tokens of the step.  8 slices are what is
+// launched: a prompt of one sequence and 16 heads of 128 x 128 leaves schedulers without a warp, but 16 slices
+// (twice the warps, each with half the state and one more exchange step a sum) measured 0.66 ms against 0.55,
+// and a warp a column with 32 slices 0.74: the exchange steps a token's update waits for cost more than the
+// idle schedulers.  A tile's rows are fetched into registers while the tile before it is
 // worked on, and put into shared memory between two barriers.  With u = k / |k| the sum along the unit key
 // is (S^T k) / |k|, so the keys themselves are staged and the token's 1 / |k| multiplies the finished sum.
-template <typename T, int RC>
+template <typename T, int RC, int SLICES>
 __global__ void __launch_bounds__(THREADS) delta_scan_kernel(DeltaStateParams p) {
+    constexpr int COLS = 4 * (32 / SLICES);         // value columns per CTA: 16 with 8 slices, 8 with 16
     constexpr int P = (RC / 4) % 2 ? RC : RC + 4;   // slice stride in floats: P / 4 odd, so the 8 slices' 16-byte reads miss each other's banks
     constexpr int ROW = SLICES * P;
     extern __shared__ __align__(16) float smem[];
@@ -124,7 +129,7 @@ __global__ void __launch_bounds__(THREADS) delta_scan_kernel(DeltaStateParams p)
     float* st_s = dot_s + TT * 4;           // [SLICES * RC][COLS + 1]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int slice = lane & 7, col = warp * 4 + (lane >> 3);
+    const int slice = lane & (SLICES - 1), col = warp * (32 / SLICES) + lane / SLICES;
     const int d = p.d, dv = p.dv, H = p.heads;
     const int h = blockIdx.y, seq = blockIdx.z;
     const int j0 = blockIdx.x * COLS;
@@ -147,7 +152,7 @@ __global__ void __launch_bounds__(THREADS) delta_scan_kernel(DeltaStateParams p)
     // Every load of a fetch is unconditional (indices clamped into the tile) and nothing is done with the
     // values until they are stored: they are all in flight at once.  What lies outside the tile or the head
     // is replaced when it is stored: a token or channel that is not there changes nothing (decay 1, keys 0).
-    T rr[PER], rk[PER], rv;
+    T rr[PER], rk[PER], rv = from_f32<T>(0.f);
     float rw[PER], rau[PER], rdot = 0.f;
     auto fetch = [&](int t0) {
         const int nt = q_len - t0 < TT ? q_len - t0 : TT;
@@ -164,8 +169,8 @@ __global__ void __launch_bounds__(THREADS) delta_scan_kernel(DeltaStateParams p)
             rw[e] = p.decay[row * p.decay_stride + h * d + c];
             rau[e] = p.remove[row * p.remove_stride + h * d + c];
         }
-        {
-            int t = tid / COLS, jj = j0 + tid % COLS;      // TT * COLS == THREADS
+        if (tid < TT * COLS) {
+            int t = tid / COLS, jj = j0 + tid % COLS;
             t = t < nt ? t : nt - 1;
             jj = jj < dv ? jj : dv - 1;
             rv = base[(int64_t)(q_start + t0 + t) * p.row_stride + p.v_off + h * dv + jj];
@@ -191,7 +196,7 @@ __global__ void __launch_bounds__(THREADS) delta_scan_kernel(DeltaStateParams p)
             au_s[at] = there ? rau[e] : 0.f;
             w_s[at] = there ? rw[e] : 1.f;
         }
-        {
+        if (tid < TT * COLS) {
             const int t = tid / COLS, jj = tid % COLS;
             v_s[tid] = (t < nt && j0 + jj < dv) ? to_f32<T>(rv) : 0.f;
         }
@@ -378,17 +383,19 @@ __global__ void __launch_bounds__(THREADS) delta_step_kernel(DeltaStateParams p)
     if (g == 0 && mine) p.out[row * p.out_stride + h * dv + j] = p2 - aur * p1 + kr * vj;
 }
 
-template <typename T, int RC>
-int launch_rc(const DeltaStateParams& p, dim3 grid, cudaStream_t stream) {
+template <typename T, int RC, int SL>
+int launch_rc(const DeltaStateParams& p, cudaStream_t stream) {
     constexpr int P = (RC / 4) % 2 ? RC : RC + 4;
-    const size_t smem = ((size_t)4 * TT * SLICES * P + 2 * TT * COLS + 4 * TT + (size_t)SLICES * RC * (COLS + 1)) * sizeof(float);
+    constexpr int CL = 4 * (32 / SL);
+    dim3 grid((p.dv + CL - 1) / CL, p.heads, p.nseq);
+    const size_t smem = ((size_t)4 * TT * SL * P + 2 * TT * CL + 4 * TT + (size_t)SL * RC * (CL + 1)) * sizeof(float);
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<T, RC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<T, RC, SL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) GB_REFUSE("delta_scan: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
-    delta_scan_kernel<T, RC><<<grid, THREADS, smem, stream>>>(p);
+    delta_scan_kernel<T, RC, SL><<<grid, THREADS, smem, stream>>>(p);
     GB_CHECK_LAUNCH("delta_scan");
     return 0;
 }
@@ -420,14 +427,14 @@ int launch(const DeltaStateParams& p, int w2_dtype, cudaStream_t stream) {
     if (p.max_q_len == 1) return launch_step<T, float, true>(p, grid, stream);
     const int rc = ((p.d + SLICES - 1) / SLICES + 3) / 4 * 4;
     switch (rc) {
-        case 4: return launch_rc<T, 4>(p, grid, stream);
-        case 8: return launch_rc<T, 8>(p, grid, stream);
-        case 12: return launch_rc<T, 12>(p, grid, stream);
-        case 16: return launch_rc<T, 16>(p, grid, stream);
-        case 20: return launch_rc<T, 20>(p, grid, stream);
-        case 24: return launch_rc<T, 24>(p, grid, stream);
-        case 28: return launch_rc<T, 28>(p, grid, stream);
-        case 32: return launch_rc<T, 32>(p, grid, stream);
+        case 4: return launch_rc<T, 4, 8>(p, stream);
+        case 8: return launch_rc<T, 8, 8>(p, stream);
+        case 12: return launch_rc<T, 12, 8>(p, stream);
+        case 16: return launch_rc<T, 16, 8>(p, stream);
+        case 20: return launch_rc<T, 20, 8>(p, stream);
+        case 24: return launch_rc<T, 24, 8>(p, stream);
+        case 28: return launch_rc<T, 28, 8>(p, stream);
+        case 32: return launch_rc<T, 32, 8>(p, stream);
     }
     GB_REFUSE("delta_scan: %d key channels a head; at most 256", p.d);
 }

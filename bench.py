@@ -286,7 +286,7 @@ DESIGN_TWINS = {"pugalix-2k": "1.7b", "pugalix-4k": "8b", "vepitar-2k": "pugalix
 OP_CLASSES = ("gemm", "gemm_add", "gemm_swiglu", "gemm_scaled", "gemm_residual", "attention", "attention_decode_rope",
               "qk_norm_rope_kv_write", "state_scan", "head_norm_gate", "gla_decay", "add_rmsnorm", "embed_gather", "swiglu",
               "prenorm_layer_forward", "delta_scan", "conv_qkv", "attention_sigmoid", "hyper_mix_norm", "moe_route", "moe_act", "moe_rows",
-              "moe_group", "moe_gather", "moe_combine", "relu2", "tanh_")
+              "moe_rows_grouped", "moe_group", "moe_gather", "moe_combine", "relu2", "tanh_")
 
 
 class OpTimer:
@@ -524,8 +524,8 @@ def probe(name, **opts):
         if name.startswith("delta"):
             zw, za, bias = f32(rows, heads * d), f32(rows, heads * d), f32(heads * d)
 
-            def fn():
-                ops.delta_scan(rkv, 0, heads * d, 2 * heads * d, heads, d, d, zw.clone(), bias, 0.6, za.clone(), bias, 1e-6, state, out, slot, start,
+            def fn():     # the preparation kernel overwrites its pre-activations: a repeated call prepares other numbers, at the same cost
+                ops.delta_scan(rkv, 0, heads * d, 2 * heads * d, heads, d, d, zw, bias, 0.6, za, bias, 1e-6, state, out, slot, start,
                                ql, nseq, max_q_len=q_len, prepare=True)
         else:
             decay = torch.sigmoid(f32(rows, heads * d) + 3.0)

@@ -294,3 +294,5 @@ GB_API int gb_moe_gather(const void* x, int64_t x_stride, const int* src_row, vo
 GB_API int gb_relu2(void* z, int64_t n, int dtype, cudaStream_t stream);
 GB_API int gb_moe_combine(const float* ys, const int* place, const float* weight, float* out, int64_t out_stride, int rows, int top, int hidden,
                           cudaStream_t stream);
+GB_API int gb_moe_rows_grouped(const MoeRowsParams* p, const int* offsets, const int* src_row, float* ys, int dtype, int w_dtype,
+                               cudaStream_t stream);

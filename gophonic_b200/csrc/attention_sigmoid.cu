@@ -28,7 +28,14 @@ namespace {
 
 constexpr int MAX_TAPS = 8;
 typedef __nv_bfloat16 bf16;
-constexpr float LOG2E = 1.4426950408889634f;
+
+// sigmoid(z) for z given as half its argument: 0.5 + 0.5 tanh(z / 2), one special-function instruction; its error
+// (about 2^-11 relative) is below the rounding of the weight to bfloat16 that follows
+__device__ __forceinline__ float sigmoid_of_half(float half_z) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(half_z));
+    return fmaf(t, 0.5f, 0.5f);
+}
 
 // copy 64 rows of N bf16 (contiguous in global memory) into padded shared rows
 template <int N>
@@ -89,8 +96,8 @@ __global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(SigmoidAttnParams
     load_tile(t_lo, 0);
     cp_async_commit();
 
-    const float sc = p.scale * LOG2E;
-    const float bias = (p.score_bias ? p.score_bias[head] : 0.f) * LOG2E;
+    const float sc = 0.5f * p.scale;                                  // half the argument of the sigmoid: see sigmoid_of_half
+    const float bias = 0.5f * (p.score_bias ? p.score_bias[head] : 0.f);
     const int row0 = past + q0 + warp * 16 + g;  // absolute position of this thread's first row
     const int row1 = row0 + 8;
     float o[NF][4];
@@ -129,17 +136,23 @@ __global__ void __launch_bounds__(128) attn_sigmoid_mma_kernel(SigmoidAttnParams
                 mma_bf16_16816(s[jp * 2 + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b[2], b[3]);
             }
         }
-        // the weights: sigmoid(score * scale + bias) where the key is visible, by absolute position
+        // the weights: sigmoid(score * scale + bias) where the key is visible, by absolute position; a tile that
+        // every row of this warp sees whole needs no masks
+        const int wrow_lo = past + q0 + warp * 16, wrow_hi = wrow_lo + 15;
+        const bool whole = t * 64 + 63 <= wrow_lo && (p.window <= 0 || t * 64 > wrow_hi - p.window);
         uint32_t pa[4][4];
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             float w[4];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                int key = t * 64 + j * 8 + t4 * 2 + (e & 1);
-                int row = (e & 2) ? row1 : row0;
-                bool ok = key <= row && (p.window <= 0 || key > row - p.window);
-                w[e] = ok ? __fdividef(1.f, 1.f + exp2f(-fmaf(s[j][e], sc, bias))) : 0.f;
+                w[e] = sigmoid_of_half(fmaf(s[j][e], sc, bias));
+                if (!whole) {
+                    int key = t * 64 + j * 8 + t4 * 2 + (e & 1);
+                    int row = (e & 2) ? row1 : row0;
+                    bool ok = key <= row && (p.window <= 0 || key > row - p.window);
+                    w[e] = ok ? w[e] : 0.f;
+                }
             }
             pa[j >> 1][(j & 1) * 2] = pack_bf16(w[0], w[1]);
             pa[j >> 1][(j & 1) * 2 + 1] = pack_bf16(w[2], w[3]);
@@ -221,10 +234,10 @@ __global__ void __launch_bounds__(128) attn_sigmoid_decode_mma_kernel(SigmoidAtt
     load_tile(t_lo, 0);
     cp_async_commit();
 
-    const float sc = p.scale * LOG2E;
+    const float sc = 0.5f * p.scale;
     const int h0 = kvh * G + g, h1 = h0 + 8;           // the heads of this thread's two rows
-    const float bias0 = (p.score_bias && g < G ? p.score_bias[h0] : 0.f) * LOG2E;
-    const float bias1 = (p.score_bias && g + 8 < G ? p.score_bias[h1] : 0.f) * LOG2E;
+    const float bias0 = 0.5f * (p.score_bias && g < G ? p.score_bias[h0] : 0.f);
+    const float bias1 = 0.5f * (p.score_bias && g + 8 < G ? p.score_bias[h1] : 0.f);
     float o[NF][4];
 #pragma unroll
     for (int j = 0; j < NF; j++)
@@ -264,7 +277,7 @@ __global__ void __launch_bounds__(128) attn_sigmoid_decode_mma_kernel(SigmoidAtt
             for (int e = 0; e < 4; e++) {
                 const int key = t * 64 + warp * 16 + j * 8 + t4 * 2 + (e & 1);
                 const bool ok = key <= pos && (p.window <= 0 || key > pos - p.window);
-                w[e] = ok ? __fdividef(1.f, 1.f + exp2f(-fmaf(s[j][e], sc, (e & 2) ? bias1 : bias0))) : 0.f;
+                w[e] = ok ? sigmoid_of_half(fmaf(s[j][e], sc, (e & 2) ? bias1 : bias0)) : 0.f;
             }
             pa[j * 2] = pack_bf16(w[0], w[1]);
             pa[j * 2 + 1] = pack_bf16(w[2], w[3]);

@@ -166,6 +166,40 @@ __global__ void __launch_bounds__(128) moe_down_rows_kernel(MoeRowsParams p) {
     if (lane == 0) p.out[(int64_t)r * p.out_stride + c] = a;
 }
 
+// The same two products with the pairs sorted by expert (moe_group): a warp takes a hidden unit (an output column) of
+// ONE expert and walks that expert's pairs, so an expert's matrices are read from memory once however many rows chose
+// it (the row of the matrix stays in the first-level cache from pair to pair).  act[p, i] = relu(up_e[i] . x[src_row[p]])^2
+// at the pair's sorted place p, ys[p, c] = down_e[c] . act[p]; the weights are applied when the rows are added up.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) moe_up_grouped_kernel(MoeRowsParams p, const int* __restrict__ offsets, const int* __restrict__ src_row) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i = blockIdx.x * 4 + warp, e = blockIdx.y;
+    const int lo = offsets[e], hi = offsets[e + 1];
+    if (i >= p.ff || lo == hi) return;
+    const TW* w = (const TW*)p.up + ((int64_t)e * p.ff + i) * p.hidden;
+    for (int at = lo; at < hi; at++) {
+        const T* x = (const T*)p.x + (int64_t)src_row[at] * p.x_stride;
+        const float a = warp_sum(warp_dot<T, TW>(w, x, p.hidden, lane));
+        if (lane == 0) {
+            const float z = fmaxf(to_f32<T>(from_f32<T>(a)), 0.f);
+            ((T*)p.act)[(int64_t)at * p.ff + i] = from_f32<T>(z * z);
+        }
+    }
+}
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128) moe_down_grouped_kernel(MoeRowsParams p, const int* __restrict__ offsets, float* __restrict__ ys) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = blockIdx.x * 4 + warp, e = blockIdx.y;
+    const int lo = offsets[e], hi = offsets[e + 1];
+    if (c >= p.hidden || lo == hi) return;
+    const TW* w = (const TW*)p.down + ((int64_t)c * p.experts + e) * p.ff;
+    for (int at = lo; at < hi; at++) {
+        const float a = warp_sum(warp_dot<T, TW>(w, (const T*)p.act + (int64_t)at * p.ff, p.ff, lane));
+        if (lane == 0) ys[(int64_t)at * p.hidden + c] = a;
+    }
+}
+
 constexpr int GROUP_THREADS = 1024;
 constexpr int GROUP_MAX_EXPERTS = 512;
 
@@ -317,5 +351,27 @@ GB_API int gb_moe_rows(const MoeRowsParams* pp, int dtype, int w_dtype, cudaStre
         GB_REFUSE("moe_rows: activations of dtype %d with weights of dtype %d", dtype, w_dtype);
     }
     GB_CHECK_LAUNCH("moe_rows");
+    return 0;
+}
+
+// The few-row feed-forward with the pairs sorted by expert: `offsets` and `src_row` as moe_group left them, `ys`
+// float32 [rows * top, hidden] receives every pair's output at its sorted place (moe_combine adds them up).
+GB_API int gb_moe_rows_grouped(const MoeRowsParams* pp, const int* offsets, const int* src_row, float* ys, int dtype, int w_dtype,
+                               cudaStream_t stream) {
+    MoeRowsParams p = *pp;
+    if (p.rows <= 0) return 0;
+    if (p.experts <= 0 || p.experts > 65535 || p.top <= 0 || p.ff <= 0 || p.hidden <= 0) GB_REFUSE("moe_rows: %d experts, %d a token, %d x %d", p.experts, p.top, p.ff, p.hidden);
+    if (!p.x || !p.up || !p.down || !p.act || !offsets || !src_row || !ys) GB_REFUSE("moe_rows: a tensor is missing");
+    dim3 ugrid((p.ff + 3) / 4, p.experts), dgrid((p.hidden + 3) / 4, p.experts);
+    if (dtype == GB_BF16 && w_dtype == GB_BF16) {
+        moe_up_grouped_kernel<__nv_bfloat16, __nv_bfloat16><<<ugrid, 128, 0, stream>>>(p, offsets, src_row);
+        moe_down_grouped_kernel<__nv_bfloat16, __nv_bfloat16><<<dgrid, 128, 0, stream>>>(p, offsets, ys);
+    } else if (dtype == GB_F32 && w_dtype == GB_F32) {
+        moe_up_grouped_kernel<float, float><<<ugrid, 128, 0, stream>>>(p, offsets, src_row);
+        moe_down_grouped_kernel<float, float><<<dgrid, 128, 0, stream>>>(p, offsets, ys);
+    } else {
+        GB_REFUSE("moe_rows: activations of dtype %d with weights of dtype %d", dtype, w_dtype);
+    }
+    GB_CHECK_LAUNCH("moe_rows_grouped");
     return 0;
 }

@@ -1220,6 +1220,26 @@ def moe_rows(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, index: torch
     _check(_lib.gb_moe_rows(byref(p), _code(x.dtype), _code(up.dtype), _stream()), 2)
 
 
+def moe_rows_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, offsets: torch.Tensor, src_row: torch.Tensor, ys: torch.Tensor,
+                     experts: int, top: int, ff: int) -> None:
+    """The few-row feed-forward with the (row, choice) pairs sorted by expert (``offsets`` and ``src_row`` from
+    ``moe_group``): every expert's matrices are read once, ``ys`` (float32 [rows * top, hidden]) receives each pair's
+    output down_e(relu(up_e x)^2) at its sorted place; ``moe_combine`` adds a row's pairs up with their weights."""
+    _need(x, "moe x", dim=2, contiguous=False)
+    _need(up, "stacked up matrices", dim=2)
+    _need(down, "stacked down matrices", up.dtype, 2)
+    _need(ys, "expert outputs", torch.float32, 2)
+    _need(offsets, "offsets", torch.int32, 1)
+    _need(src_row, "source rows", torch.int32, 1)
+    rows, hidden = x.shape
+    if (up.shape != (experts * ff, hidden) or down.shape != (hidden, experts * ff) or ys.shape != (rows * top, hidden) or x.stride(1) != 1
+            or offsets.numel() < experts + 1 or src_row.numel() < rows * top):
+        raise KernelError(f"moe_rows_grouped: x {tuple(x.shape)}, up {tuple(up.shape)}, down {tuple(down.shape)}, outputs {tuple(ys.shape)}")
+    act = torch.empty((rows * top, ff), dtype=x.dtype, device=x.device)
+    p = _MoeRowsParams(x.data_ptr(), x.stride(0), up.data_ptr(), down.data_ptr(), act.data_ptr(), 0, 0, 0, 0, rows, experts, top, ff, hidden)
+    _check(_lib.gb_moe_rows_grouped(byref(p), _ptr(offsets), _ptr(src_row), _ptr(ys), _code(x.dtype), _code(up.dtype), _stream()), 2)
+
+
 def moe_group(index: torch.Tensor, experts: int, offsets: torch.Tensor, place: torch.Tensor, src_row: torch.Tensor) -> None:
     """Sort the (row, choice) pairs of ``index`` (int32 [rows, top]) by expert: ``offsets`` (int32 [experts + 1]) receives
     where each expert's group starts, ``place`` (int32 [rows * top]) each pair's position in the sorted order and

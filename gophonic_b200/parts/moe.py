@@ -7,7 +7,9 @@ down matrices side by side.  A step of many rows runs two products over the stac
 for each expert (zero where it was not chosen) folded into the activation between them, so the experts a
 token did not choose contribute exact zeros and nothing depends on where the rows of an expert lie; such
 a step stays free of host reads, so single-token steps of many sequences replay from a graph.  A step of
-few rows reads only the chosen experts' matrices (``ops.moe_rows``).  A prompt-sized step, which is never
+few rows reads only the chosen experts' matrices (``ops.moe_rows``; with more (row, choice) pairs than
+experts the pairs are sorted by expert on the device first, so that an expert's matrices are read once:
+``ops.moe_rows_grouped``).  A prompt-sized step, which is never
 replayed from a graph, sorts its (row, choice) pairs by expert, reads the experts' group sizes on the host
 and runs one pair of products an expert on that expert's rows alone, so it does top / experts of the stacked
 path's arithmetic.
@@ -60,7 +62,18 @@ class MoE(FeedForward):
         weight = torch.empty((rows, s.top), dtype=torch.float32, device=x.device)
         ops.moe_route(logits, s.top, float(s.renorm_eps), dense, index, weight)
         if rows <= self.ROWS_SPARSE and s.top < s.experts:
-            ops.moe_rows(x, self.up, self.down, index, weight, out, s.experts, s.intermediate)
+            if rows * s.top <= s.experts:      # hardly two pairs with one expert: a pair reads its expert's matrices
+                ops.moe_rows(x, self.up, self.down, index, weight, out, s.experts, s.intermediate)
+                return
+            # more pairs than experts: sorted by expert on the device, every expert's matrices are read once
+            pairs = rows * s.top
+            offsets = torch.empty(s.experts + 1, dtype=torch.int32, device=x.device)
+            place = torch.empty(pairs, dtype=torch.int32, device=x.device)
+            src_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
+            ops.moe_group(index, s.experts, offsets, place, src_row)
+            ys = torch.empty((pairs, s.hidden), dtype=torch.float32, device=x.device)
+            ops.moe_rows_grouped(x, self.up, self.down, offsets, src_row, ys, s.experts, s.top, s.intermediate)
+            ops.moe_combine(ys, place, weight, out)
             return
         if rows >= self.ROWS_GROUPED and s.top < s.experts and not torch.cuda.is_current_stream_capturing():
             self._grouped(x, index, weight, out)

@@ -512,7 +512,7 @@ def test_router_and_experts(shape):
     tensors = {n: torch.tensor(a, dtype=torch.float32, device=dev) for n, a in w.items()}
     w = {n: t.cpu().numpy().astype(np.float64) for n, t in tensors.items()}
     part = MoE(spec, "", tensors, Runtime(dev, torch.float32, ops))
-    for rows in (3, 50, 300):              # few rows read the chosen experts only, more run the stacked products, many every expert on its own rows
+    for rows in (1, 3, 12, 50, 300):              # few rows read the chosen experts only (pair by pair, or sorted by expert), more run the stacked products, many every expert on its own rows
         h = rng.standard_normal((rows, width)).astype(np.float32)
         out = torch.empty((rows, width), dtype=torch.float32, device=dev)
         part.forward(None, torch.tensor(h, device=dev), out)

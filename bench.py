@@ -285,7 +285,7 @@ def further_model_points(name, steps, torch, ops, hbm_peak, tflops_peak):
 DESIGN_TWINS = {"pugalix-2k": "1.7b", "pugalix-4k": "8b", "vepitar-2k": "pugalix-2k", "vepitar-4k": "pugalix-4k"}
 OP_CLASSES = ("gemm", "gemm_add", "gemm_swiglu", "gemm_scaled", "gemm_residual", "attention", "attention_decode_rope",
               "qk_norm_rope_kv_write", "state_scan", "head_norm_gate", "gla_decay", "add_rmsnorm", "embed_gather", "swiglu",
-              "prenorm_layer_forward", "delta_scan", "conv_qkv", "attention_sigmoid", "hyper_mix_norm", "moe_route", "moe_act", "moe_rows",
+              "prenorm_layer_forward", "embed_streams", "delta_scan", "conv_qkv", "attention_sigmoid", "hyper_mix_norm", "moe_route", "moe_act", "moe_rows",
               "moe_rows_grouped", "moe_group", "moe_gather", "moe_combine", "relu2", "tanh_")
 
 

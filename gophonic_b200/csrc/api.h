@@ -194,6 +194,8 @@ struct HyperParams {
     const int* row_index;    // rows to read (x_out row i from streams row row_index[i]), or null
 };
 GB_API int gb_hyper_mix_norm(const HyperParams* p, int out_dtype, cudaStream_t stream);
+GB_API int gb_embed_streams(const void* table, int table_dtype, const int* ids, int rows, int hidden, int vocab, float* streams,
+                            int64_t stream_stride, int n_streams, float scale, cudaStream_t stream);
 
 // The generalized delta rule: S <- diag(w) S - (a u)(u^T S) + k v^T, o = S^T r per (sequence, head).
 struct DeltaStateParams {

@@ -26,7 +26,7 @@
 
 namespace {
 
-constexpr int MAX_TAPS = 8;
+constexpr int MAX_TAPS = 16;
 typedef __nv_bfloat16 bf16;
 
 // sigmoid(z) for z given as half its argument: 0.5 + 0.5 tanh(z / 2), one special-function instruction; its error

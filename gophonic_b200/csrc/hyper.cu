@@ -83,6 +83,20 @@ __global__ void __launch_bounds__(HC_MAX_THREADS) hyper_mix_norm_kernel(HyperPar
     for (int c = tid; c < p.width; c += HC_THREADS) o[c] = from_f32<TO>(u_s[c] * inv * p.norm_w[c]);
 }
 
+// streams[s][r, :] = float32(table[ids[r], :]) * scale for every stream s: all streams start as the embedding output
+template <typename T>
+__global__ void embed_streams_kernel(const T* __restrict__ table, const int* __restrict__ ids, int hidden, int vocab, float* __restrict__ streams,
+                                     int64_t stream_stride, int n_streams, float scale) {
+    const int r = blockIdx.x;
+    int id = ids[r];
+    if (!gb_check(id, vocab, GB_CHECK_TOKEN_ID) || id < 0 || id >= vocab) id = 0;   // ids are validated on the host
+    const T* src = table + (int64_t)id * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = to_f32<T>(src[i]) * scale;   // scale 1 changes no bit
+        for (int s = 0; s < n_streams; s++) streams[s * stream_stride + (int64_t)r * hidden + i] = v;
+    }
+}
+
 template <typename TO, int S>
 int launch_s(const HyperParams& p, cudaStream_t stream) {
     const size_t smem = p.x_out ? (size_t)p.width * sizeof(float) : 0;
@@ -127,3 +141,21 @@ GB_API int gb_hyper_mix_norm(const HyperParams* pp, int out_dtype, cudaStream_t 
     if (out_dtype == GB_BF16) return launch<__nv_bfloat16>(p, stream);
     GB_REFUSE("hyper_mix_norm: unknown dtype %d", out_dtype);
 }
+
+GB_API int gb_embed_streams(const void* table, int table_dtype, const int* ids, int rows, int hidden, int vocab, float* streams,
+                            int64_t stream_stride, int n_streams, float scale, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || vocab <= 0 || n_streams <= 0) GB_REFUSE("embed_streams: hidden %d, vocab %d, %d streams", hidden, vocab, n_streams);
+    if (table_dtype == GB_F32)
+        embed_streams_kernel<float><<<rows, 256, 0, stream>>>((const float*)table, ids, hidden, vocab, streams, stream_stride, n_streams, scale);
+    else if (table_dtype == GB_BF16)
+        embed_streams_kernel<__nv_bfloat16><<<rows, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, hidden, vocab, streams, stream_stride,
+                                                                      n_streams, scale);
+    else
+        GB_REFUSE("embed_streams: unknown table dtype %d", table_dtype);
+    GB_CHECK_LAUNCH("embed_streams");
+    return 0;
+}
+
+// the checked build's record of the first index this file's kernels found out of bounds
+GB_CHECK_READER(gb_checked_status_hyper)

@@ -189,8 +189,7 @@ class Model:
         rows, S = batch.rows, self.streams
         streams = torch.empty((S, rows, self.spec.hidden), dtype=torch.float32, device=self.rt.device)
         scale = float(getattr(self.spec.embedding, "scale", 1.0))
-        for s in range(S):
-            ops.embed_gather(self.embedding, batch.ids, streams[s], scale=scale)
+        ops.embed_streams(self.embedding, batch.ids, streams, scale=scale)
         pending = None
         for pos, entry in enumerate(self.spec.schedule):
             pending = self.blocks[entry.layer].forward(batch, streams, pending, cache.view(pos))

@@ -471,7 +471,7 @@ def checked_status():
     found out of bounds since the last call (the access was skipped or redirected, nothing faulted).
     Always None in the ordinary build, whose kernels carry no checks.  Synchronises."""
     out = (c_int * 4)()
-    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5", "linear_state", "delta_state", "attention_sigmoid"):
+    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5", "linear_state", "delta_state", "attention_sigmoid", "hyper"):
         code = int(getattr(_lib, "gb_checked_status_" + name)(out))
         if code or out[3]:
             return name, _CHECK_NAMES.get(code, f"code {code}"), out[1], out[2], out[3]
@@ -943,6 +943,18 @@ class _HyperParams(Structure):
         ("y", c_void_p), ("mix", c_void_p), ("out_coef", c_void_p), ("mult", c_float), ("in_coef", c_void_p),
         ("norm_w", c_void_p), ("eps", c_float), ("x_out", c_void_p), ("row_index", c_void_p),
     ]
+
+
+def embed_streams(table: torch.Tensor, ids: torch.Tensor, streams: torch.Tensor, scale: float = 1.0) -> None:
+    """streams[s, r, :] = float32(table[ids[r], :]) * scale for every stream s (``streams`` float32 [S, rows, hidden])."""
+    _need(table, "embed table", dim=2)
+    _need(ids, "ids", torch.int32, 1)
+    _need(streams, "streams", torch.float32, 3)
+    S, rows, hidden = streams.shape
+    if ids.numel() != rows or table.shape[1] != hidden:
+        raise KernelError(f"embed_streams: {ids.numel()} ids, table {tuple(table.shape)}, streams {tuple(streams.shape)}")
+    _check(_lib.gb_embed_streams(_ptr(table), _code(table.dtype), _ptr(ids), c_int(rows), c_int(hidden), c_int(table.shape[0]), _ptr(streams),
+                                 c_int64(streams.stride(0)), c_int(S), c_float(scale), _stream()))
 
 
 def hyper_mix_norm(streams: torch.Tensor, y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,

@@ -263,7 +263,7 @@ struct SigmoidAttnParams : AttnParamsX {
     const void* gate;          // [rows, gate_stride] (activation dtype): heads pre-activations, or null
     int64_t gate_stride;
 };
-GB_API int gb_attention_sigmoid(const SigmoidAttnParams* p, int dtype, cudaStream_t stream);
+GB_API int gb_attention_sigmoid(const SigmoidAttnParams* p, int dtype, int rows, cudaStream_t stream);
 
 // Mixture of experts.
 struct MoeRouteParams {

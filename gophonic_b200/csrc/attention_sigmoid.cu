@@ -655,7 +655,10 @@ GB_API int gb_conv_qkv(const ConvQkvParams* pp, int dtype, cudaStream_t stream) 
     GB_REFUSE("conv_qkv: unknown dtype %d", dtype);
 }
 
-GB_API int gb_attention_sigmoid(const SigmoidAttnParams* pp, int dtype, cudaStream_t stream) {
+int gb_attention_sigmoid_tc5(const SigmoidAttnParams* pp, int rows, int pages, cudaStream_t stream);
+
+// rows: packed query rows in the q buffer (the tcgen05 kernel's tensor map spans them); 0: not known
+GB_API int gb_attention_sigmoid(const SigmoidAttnParams* pp, int dtype, int rows, cudaStream_t stream) {
     SigmoidAttnParams p = *pp;
     if (p.nseq <= 0 || p.max_q_len <= 0) return 0;
     if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("attention: %d heads over %d kv heads", p.heads, p.kv_heads);
@@ -664,6 +667,13 @@ GB_API int gb_attention_sigmoid(const SigmoidAttnParams* pp, int dtype, cudaStre
     if (p.dv < 0 || p.dv > 256) GB_REFUSE("attention_sigmoid: value size %d is outside [1, 256]", p.dv);
     if (dtype == GB_F32) return launch<float>(p, stream);
     const int dv = p.dv > 0 ? p.dv : p.d;
+    // prompts of heads of 128: the tcgen05 kernel, as for the softmax (num_splits -2 asks for mma.sync instead)
+    if (dtype == GB_BF16 && p.num_splits == 1 && p.d == 128 && dv == 128 && rows > 0 && p.max_q_len >= 65 && !((uintptr_t)p.q & 15) &&
+        !(p.q_row_stride & 7) && !((uintptr_t)p.out & 15) && !(p.out_row_stride & 7)) {
+        p.dv = 0;
+        return gb_attention_sigmoid_tc5(&p, rows, p.pages, stream);
+    }
+    if (p.num_splits == -2) p.num_splits = 1;
     if (dtype == GB_BF16 && p.num_splits != -1 && mma_takes(p, dv)) {     // num_splits -1 asks for the CUDA-core kernel
         switch (p.d) {
             case 32: return launch_mma<32>(p, dv, stream);

@@ -157,8 +157,8 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 
 __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                    const __grid_constant__ CUtensorMap map_k,
-                                                                   const __grid_constant__ CUtensorMap map_v, AttnParamsX p,
-                                                                   int by_kv_head) {
+                                                                   const __grid_constant__ CUtensorMap map_v, SigmoidAttnParams p,
+                                                                   int by_kv_head, int sigmoid) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = base;                          // [GROUPS][Q_BYTES]
@@ -396,7 +396,12 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
         const bool row_ok = qrow < q_len;
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         const uint32_t o_addr = tmem_base + lane_addr + (uint32_t)(256 + g * 128);
-        const float sc = p.scale * LOG2E;
+        // With sigmoid weights (the other form this kernel takes) a visible key weighs sigmoid(score * scale + bias of the
+        // head): there is no maximum, no sum and no rescaling, the weights go the same way into tensor memory, and at the
+        // end the row is multiplied by its head's gate instead of divided by a sum.  The sigmoid is 0.5 + 0.5 tanh(z / 2).
+        const bool sig = sigmoid != 0;
+        const float sc = sig ? 0.5f * p.scale : p.scale * LOG2E;
+        const float half_bias = sig && p.score_bias ? 0.5f * p.score_bias[head] : 0.f;
         const int my_n = n_g[g];
         float m_run = -INFINITY;   // true running maximum (scaled, base 2)
         float m_used = -INFINITY;  // the maximum the probabilities and O are currently scaled by
@@ -424,16 +429,19 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                     if (kb > pos || (p.window > 0 && kb <= pos - p.window && kb >= p.keep_first)) v1[i] = 0xff800000u;
                 }
             }
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            bool grow = false;
+            if (!sig) {
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
+                for (int i = 0; i < 32; i += 4) {
 #pragma unroll
-                for (int e = 0; e < 4; e++) mx[e] = max3(mx[e], __uint_as_float(v0[i + e]), __uint_as_float(v1[i + e]));
+                    for (int e = 0; e < 4; e++) mx[e] = max3(mx[e], __uint_as_float(v0[i + e]), __uint_as_float(v1[i + e]));
+                }
+                const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;  // sc > 0
+                m_run = fmaxf(m_run, tile_max);
+                // rescale only when the maximum has outgrown the scale in use (or there is none yet)
+                grow = m_run > m_used + RESCALE_AT || (m_used == -INFINITY && m_run != -INFINITY);
             }
-            const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * sc;  // sc > 0
-            m_run = fmaxf(m_run, tile_max);
-            // rescale only when the maximum has outgrown the scale in use (or there is none yet)
-            const bool grow = m_run > m_used + RESCALE_AT || (m_used == -INFINITY && m_run != -INFINITY);
             // this page's probability buffer was read by the product of two pages ago
             if (!mbar_wait(&o_done[g][b], ((uint32_t)(j >> 1) & 1u) ^ 1u)) {
                 ok = false;
@@ -461,7 +469,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             }
             if (grow) m_used = m_run;
             const float mbase = m_used == -INFINITY ? 0.f : m_used;
-            const uint64_t sc2 = pack2(sc, sc), nmb2 = pack2(-mbase, -mbase);
+            const uint64_t sc2 = pack2(sc, sc), nmb2 = sig ? pack2(half_bias, half_bias) : pack2(-mbase, -mbase);
             uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
             uint32_t pw[32];  // the row's 64 probabilities, two a word
 #pragma unroll
@@ -473,7 +481,12 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                     const uint32_t a = c < 4 ? v0[i] : v1[i], bb = c < 4 ? v0[i + 1] : v1[i + 1];
                     float t0, t1, p0, p1;
                     unpack2(fma2(pack2(__uint_as_float(a), __uint_as_float(bb)), sc2, nmb2), t0, t1);
-                    if (e < POLY_PAIRS) {
+                    if (sig) {      // a masked key (-inf) weighs nothing
+                        asm("tanh.approx.f32 %0, %1;" : "=f"(p0) : "f"(t0));
+                        asm("tanh.approx.f32 %0, %1;" : "=f"(p1) : "f"(t1));
+                        p0 = a == 0xff800000u ? 0.f : fmaf(p0, 0.5f, 0.5f);
+                        p1 = bb == 0xff800000u ? 0.f : fmaf(p1, 0.5f, 0.5f);
+                    } else if (e < POLY_PAIRS) {
                         exp2_poly_x2(t0, t1, p0, p1);
                     } else {
                         p0 = fast_exp2(t0);
@@ -505,8 +518,13 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             // a sink adds one unit to the denominator: a key of score 0, in the scale the sums are kept in
             // (a sum so scaled that the unit overflows gives 1 / inf = 0, which is the limit)
-            if (p.sink && m_used != -INFINITY) l += exp2f(-m_used);
-            const float inv = 1.f / l;
+            if (!sig && p.sink && m_used != -INFINITY) l += exp2f(-m_used);
+            float inv = 1.f / l;
+            if (sig) {
+                inv = 1.f;
+                if (p.gate && row_ok)
+                    inv = 1.f / (1.f + expf(-__bfloat162float(((const bf16*)p.gate)[(int64_t)(q_start + qrow) * p.gate_stride + head])));
+            }
             bf16* op = (bf16*)p.out + (int64_t)(q_start + qrow) * p.out_row_stride + (int64_t)head * HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
@@ -561,10 +579,27 @@ GB_API int gb_attention_prefill_tc5(const AttnParams* pp, int rows, int pages, c
     return gb_attention_prefill_tc5_x(&x, rows, pages, stream);
 }
 
+static int launch_tc5(const SigmoidAttnParams& p, int rows, int pages, int sigmoid, cudaStream_t stream);
+
 GB_API int gb_attention_prefill_tc5_x(const AttnParamsX* pp, int rows, int pages, cudaStream_t stream) {
-    AttnParamsX p = *pp;
+    SigmoidAttnParams p;
+    static_cast<AttnParamsX&>(p) = *pp;
+    p.score_bias = nullptr;
+    p.gate = nullptr;
+    p.gate_stride = 0;
+    return launch_tc5(p, rows, pages, 0, stream);
+}
+
+// The same kernel with sigmoid weights (a bias a head on the score, a gate a head on the output), for the prompts of
+// the attention that does not normalise over the keys.
+int gb_attention_sigmoid_tc5(const SigmoidAttnParams* pp, int rows, int pages, cudaStream_t stream) {
+    if (pp->keep_first || pp->sink) GB_REFUSE("attention_sigmoid_tc5: kept first tokens and a sink belong to the softmax");
+    return launch_tc5(*pp, rows, pages, 1, stream);
+}
+
+static int launch_tc5(const SigmoidAttnParams& p, int rows, int pages, int sigmoid, cudaStream_t stream) {
     if (p.nseq <= 0 || p.max_q_len <= 0) return 0;
-    const char* who = "attention_prefill_tc5";
+    const char* who = sigmoid ? "attention_sigmoid_tc5" : "attention_prefill_tc5";
     if (p.d != HD) GB_REFUSE("%s: head_dim %d; this kernel takes 128", who, p.d);
     if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("%s: %d heads over %d kv heads", who, p.heads, p.kv_heads);
     if (p.num_splits != 1) GB_REFUSE("%s: key splits are for single-token rows", who);
@@ -591,7 +626,7 @@ GB_API int gb_attention_prefill_tc5_x(const AttnParamsX* pp, int rows, int pages
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("%s: grid (%u, %u, %u) exceeds one launch", who, grid.x, grid.y, grid.z);
     // keys and values of the longest prompt, all kv heads: more than 48 MB do not stay in L2 beside the rest
     const int by_kv_head = (int64_t)p.max_q_len * p.kv_heads * (4 * HD) > ((int64_t)48 << 20) ? 1 : 0;
-    cudaError_t e = launch_pdl(attn_prefill_tc5_kernel, grid, dim3(THREADS), (size_t)smem, stream, map_q, map_k, map_v, p, by_kv_head);
+    cudaError_t e = launch_pdl(attn_prefill_tc5_kernel, grid, dim3(THREADS), (size_t)smem, stream, map_q, map_k, map_v, p, by_kv_head, sigmoid);
     if (e != cudaSuccess) GB_REFUSE("%s: launch failed: %s", who, cudaGetErrorString(e));
     return 0;
 }

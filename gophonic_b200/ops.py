@@ -1143,9 +1143,10 @@ def attention_sigmoid(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor,
     that are not normalised over the keys; ``window`` > 0: row i sees keys j with 0 <= i - j < window.  With
     ``gate`` ([rows, heads] pre-activations, a view with a free row stride) head h's output is multiplied by
     sigmoid(gate[row, h]).  out is [rows, heads * value_dim].  bfloat16 rows with key heads of 32, 64, 96 or
-    128 and value heads of 32, 48, 64 or 128 run on the tensor cores, everything else (and ``algo`` "simt")
-    on the CUDA cores."""
-    if algo not in ("auto", "simt"):
+    128 and value heads of 32, 48, 64 or 128 run on the tensor cores (prompts of 65 rows and more with heads of
+    128 on the tcgen05 kernel, the rest on mma.sync; ``algo`` "mma" asks for mma.sync), everything else (and
+    ``algo`` "simt") on the CUDA cores."""
+    if algo not in ("auto", "simt", "mma"):
         raise KernelError(f"attention_sigmoid: unknown algorithm '{algo}'")
     a = _attn_params(q, out, k_plane, v_plane, block_table, batch.seq_slot, batch.seq_q_start, batch.seq_q_len, batch.seq_kv_len,
                      batch.nseq, batch.max_q_len, heads, kv_heads, head_dim, scale, window, 1, None, value_dim)
@@ -1167,7 +1168,9 @@ def attention_sigmoid(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor,
     p.gate_stride = gstride
     if algo == "simt":
         p.num_splits = -1
-    _check(_lib.gb_attention_sigmoid(byref(p), _code(q.dtype), _stream()))
+    elif algo == "mma":
+        p.num_splits = -2
+    _check(_lib.gb_attention_sigmoid(byref(p), _code(q.dtype), c_int(q.shape[0]), _stream()))
 
 
 # ---- mixture of experts -----------------------------------------------------------------------

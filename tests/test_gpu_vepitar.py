@@ -289,7 +289,7 @@ def _attention_case(rng, T, heads, kv_heads, d, dv, window):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("algo", ["auto", "simt"])
+@pytest.mark.parametrize("algo", ["auto", "mma", "simt"])
 @pytest.mark.parametrize("shape", [(2, 1, 16, 8, 37), (4, 4, 24, 24, 70), (3, 1, 8, 40, 64), (4, 2, 32, 32, 65), (2, 1, 64, 64, 1),
                                    (3, 3, 128, 128, 130), (2, 2, 16, 16, 0), (4, 1, 96, 32, 40), (2, 2, 64, 48, 200), (2, 1, 32, 128, 0)])
 def test_attention_kernel_at_the_edges(shape, dtype, algo):

@@ -155,10 +155,11 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
+template <bool SIGMOID>
 __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                    const __grid_constant__ CUtensorMap map_k,
                                                                    const __grid_constant__ CUtensorMap map_v, SigmoidAttnParams p,
-                                                                   int by_kv_head, int sigmoid) {
+                                                                   int by_kv_head) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* Qs = base;                          // [GROUPS][Q_BYTES]
@@ -399,7 +400,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
         // With sigmoid weights (the other form this kernel takes) a visible key weighs sigmoid(score * scale + bias of the
         // head): there is no maximum, no sum and no rescaling, the weights go the same way into tensor memory, and at the
         // end the row is multiplied by its head's gate instead of divided by a sum.  The sigmoid is 0.5 + 0.5 tanh(z / 2).
-        const bool sig = sigmoid != 0;
+        constexpr bool sig = SIGMOID;      // a form of its own each, so that neither carries the other's registers
         const float sc = sig ? 0.5f * p.scale : p.scale * LOG2E;
         const float half_bias = sig && p.score_bias ? 0.5f * p.score_bias[head] : 0.f;
         const int my_n = n_g[g];
@@ -614,7 +615,8 @@ static int launch_tc5(const SigmoidAttnParams& p, int rows, int pages, int sigmo
     const int smem = GROUPS * Q_BYTES + STAGES * STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_tc5_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) GB_REFUSE("%s: cannot reserve %d bytes of shared memory: %s", who, smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -626,7 +628,8 @@ static int launch_tc5(const SigmoidAttnParams& p, int rows, int pages, int sigmo
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("%s: grid (%u, %u, %u) exceeds one launch", who, grid.x, grid.y, grid.z);
     // keys and values of the longest prompt, all kv heads: more than 48 MB do not stay in L2 beside the rest
     const int by_kv_head = (int64_t)p.max_q_len * p.kv_heads * (4 * HD) > ((int64_t)48 << 20) ? 1 : 0;
-    cudaError_t e = launch_pdl(attn_prefill_tc5_kernel, grid, dim3(THREADS), (size_t)smem, stream, map_q, map_k, map_v, p, by_kv_head, sigmoid);
+    cudaError_t e = sigmoid ? launch_pdl(attn_prefill_tc5_kernel<true>, grid, dim3(THREADS), (size_t)smem, stream, map_q, map_k, map_v, p, by_kv_head)
+                            : launch_pdl(attn_prefill_tc5_kernel<false>, grid, dim3(THREADS), (size_t)smem, stream, map_q, map_k, map_v, p, by_kv_head);
     if (e != cudaSuccess) GB_REFUSE("%s: launch failed: %s", who, cudaGetErrorString(e));
     return 0;
 }

@@ -533,6 +533,28 @@ def test_router_and_experts(shape):
     close(dense.cpu().numpy(), full, 1e-6)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_products_with_a_block_of_columns_as_weights(dtype):
+    """An expert's down matrix is a block of columns of the stacked one: the product takes the wider matrix's row stride,
+    for one row as for hundreds (an expert few rows chose)."""
+    import torch
+    from gophonic_b200 import ops
+    ops.use_device(0)
+    dev = torch.device("cuda:0")
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    rng = np.random.default_rng(3)
+    N, K, wide = 72, 40, 5 * 40
+    w_all = torch.tensor(rng.standard_normal((N, wide)) / np.sqrt(K), dtype=torch.float32).to(td).to(dev)
+    for M in (1, 5, 130, 200, 300):
+        a = torch.tensor(rng.standard_normal((M, K)), dtype=torch.float32).to(td).to(dev)
+        for block in (0, 3):
+            w = w_all[:, block * K:(block + 1) * K]
+            out = torch.empty((M, N), dtype=torch.float32, device=dev)
+            ops.gemm_w_cols(a, w, out)
+            want = a.float().cpu().numpy().astype(np.float64) @ w.float().cpu().numpy().astype(np.float64).T
+            close(out.cpu().numpy(), want, 2e-5 if dtype == "float32" else 2e-3)
+
+
 # ---- generation through the entry point -----------------------------------------------------------
 @pytest.mark.parametrize("fmt", ["f32", "bf16"])
 def test_greedy_generation_through_the_entry_point(models, fmt):
